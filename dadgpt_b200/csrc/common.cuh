@@ -1,0 +1,83 @@
+// Shared host/device helpers for the dadattn kernels (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "dadattn.h"
+
+namespace dadattn {
+
+// Thread-local error text behind dadattn_last_error().
+char* error_buffer();
+int fail(int code, const char* fmt, ...);
+
+#define DAD_CUDA(call)                                                                  \
+  do {                                                                                  \
+    cudaError_t e_ = (call);                                                            \
+    if (e_ != cudaSuccess)                                                              \
+      return ::dadattn::fail(DADATTN_E_CUDA, "%s failed: %s (%s:%d)", #call,            \
+                             cudaGetErrorString(e_), __FILE__, __LINE__);               \
+  } while (0)
+
+#define DAD_LAUNCH_CHECK(name)                                                          \
+  do {                                                                                  \
+    cudaError_t e_ = cudaGetLastError();                                                \
+    if (e_ != cudaSuccess)                                                              \
+      return ::dadattn::fail(DADATTN_E_CUDA, "launch of %s failed: %s", name,           \
+                             cudaGetErrorString(e_));                                   \
+  } while (0)
+
+// Device-side sticky status word (one per device that loads the library). Kernels record a
+// DADATTN_E_* code here instead of trapping; dadattn_device_status() reads and clears it.
+int* device_status_word();  // device pointer for the current device, nullptr on failure
+
+// ---- Philox4x32-10 with cuRAND's curand_init(seed, subsequence, offset) counter set-up -------
+// The reference draws one uniform per attention probability with subsequence = flat element
+// index (cuda/gpu_ops.cu:712-727). key = seed; counter = {offset/4 (64 bit), subsequence}.
+struct PhiloxKey {
+  uint32_t k0, k1;       // seed
+  uint32_t c0, c1;       // offset / 4
+  uint32_t word;         // offset % 4
+};
+
+__host__ __device__ inline PhiloxKey make_philox(uint64_t seed, uint64_t offset) {
+  PhiloxKey p;
+  p.k0 = static_cast<uint32_t>(seed);
+  p.k1 = static_cast<uint32_t>(seed >> 32);
+  p.c0 = static_cast<uint32_t>(offset >> 2);
+  p.c1 = static_cast<uint32_t>(offset >> 34);
+  p.word = static_cast<uint32_t>(offset & 3);
+  return p;
+}
+
+__device__ __forceinline__ uint32_t philox_draw(const PhiloxKey& p, uint64_t subsequence) {
+  uint32_t c0 = p.c0, c1 = p.c1, c2 = static_cast<uint32_t>(subsequence),
+           c3 = static_cast<uint32_t>(subsequence >> 32);
+  uint32_t k0 = p.k0, k1 = p.k1;
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    uint32_t n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
+    c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return p.word == 0 ? c0 : p.word == 1 ? c1 : p.word == 2 ? c2 : c3;
+}
+
+// true = keep. Same float arithmetic as curand_uniform followed by the reference's `r < rate`.
+__device__ __forceinline__ bool philox_keep(const PhiloxKey& p, uint64_t subsequence,
+                                            float rate) {
+  float u = fmaf(static_cast<float>(philox_draw(p, subsequence)), 2.3283064e-10f,
+                 2.3283064e-10f / 2.0f);
+  return !(u < rate);
+}
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+}  // namespace dadattn

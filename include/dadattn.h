@@ -1,0 +1,142 @@
+/*
+ * dadattn — C ABI of the B200 (sm_100a) causal-attention library for DadGPT.
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues work on the given CUDA
+ * stream (pass NULL for the legacy default stream, which is what DadGPT itself uses) and
+ * returns without synchronising. Return value: 0 on success, a negative DADATTN_E_* code
+ * otherwise; dadattn_last_error() then describes the failure (thread-local string).
+ * The library allocates nothing unless a function's comment says so; all buffers belong to the
+ * caller. There is no CPU fallback: without a CUDA device every compute call fails.
+ *
+ * Tensor layouts follow DadGPT: heads already split, [BH, S, D] contiguous, row-major;
+ * lse / delta are [BH, S] fp32. "bf16" pointers are raw 16-bit bfloat16 (uint16_t here so the
+ * header needs no CUDA include).
+ */
+#ifndef DADATTN_H_
+#define DADATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DADATTN_OK 0
+#define DADATTN_E_ARG (-1)         /* null pointer, non-positive size, misaligned pointer */
+#define DADATTN_E_UNSUPPORTED (-2) /* head dimension or size outside what the kernels cover */
+#define DADATTN_E_CUDA (-3)        /* a CUDA runtime/driver call failed */
+#define DADATTN_E_TIMEOUT (-4)     /* a bounded device-side wait ran out (see dadattn_device_status) */
+#define DADATTN_E_WORKSPACE (-5)   /* workspace too small */
+
+typedef void* dadattn_stream_t; /* cudaStream_t */
+
+const char* dadattn_last_error(void);
+/* Library/kernels version string, e.g. "dadattn 0.1 sm_100a". */
+const char* dadattn_version(void);
+
+/* ---- fp32 drop-in path ---------------------------------------------------------------- */
+
+/* Replaces gpu_flash_attention_supported (reference cuda/gpu_ops.cuh:115, cuda/attention.cu:232).
+ * Returns 1 for the head sizes the fp32 kernels cover: 16, 32, 64, 128. */
+int dadattn_flash_supported(int d_head);
+
+/* Replaces gpu_flash_attention_forward (reference cuda/gpu_ops.cuh:116-117,
+ * cuda/attention.cu:234-239): out = softmax(causal(q k^T * scale)) v, lse = rowmax + ln(rowsum)
+ * of the scaled scores. q,k,v,out: [BH,S,d_head] fp32; lse: [BH,S] fp32. */
+int dadattn_flash_fwd_f32(float* out, float* lse, const float* q, const float* k, const float* v,
+                          int BH, int S, int d_head, float scale, dadattn_stream_t stream);
+
+/* Replaces gpu_flash_attention_backward (reference cuda/gpu_ops.cuh:118-122,
+ * cuda/attention.cu:241-252). Writes (does not accumulate) dq, dk, dv; delta: [BH,S] scratch
+ * owned by the caller, overwritten. */
+int dadattn_flash_bwd_f32(float* dq, float* dk, float* dv, float* delta, const float* dout,
+                          const float* out, const float* lse, const float* q, const float* k,
+                          const float* v, int BH, int S, int d_head, float scale,
+                          dadattn_stream_t stream);
+
+/* The same two calls with attention-probability dropout fused in, reproducing the reference's
+ * materialized branch (src/model.cpp:406-415 forward, :595-602 backward; mask from
+ * dropout_forward_kernel, cuda/gpu_ops.cu:712-727): score element (bh,r,c) is dropped iff the
+ * Philox4x32-10 uniform of subsequence ((unit0+bh)*S + r)*S + c, offset `offset`, seed `seed`
+ * is < rate; kept probabilities are scaled by 1/(1-rate) after normalisation; lse is that of the
+ * undropped softmax. rate = 0 gives exactly the calls above. unit0 is the global index of the
+ * first (batch,head) unit of this call (0 unless the BH axis is sharded). */
+int dadattn_flash_fwd_f32_dropout(float* out, float* lse, const float* q, const float* k,
+                                  const float* v, int BH, int S, int d_head, float scale,
+                                  float rate, uint64_t seed, uint64_t offset, int64_t unit0,
+                                  dadattn_stream_t stream);
+int dadattn_flash_bwd_f32_dropout(float* dq, float* dk, float* dv, float* delta,
+                                  const float* dout, const float* out, const float* lse,
+                                  const float* q, const float* k, const float* v, int BH, int S,
+                                  int d_head, float scale, float rate, uint64_t seed,
+                                  uint64_t offset, int64_t unit0, dadattn_stream_t stream);
+
+/* ---- dropout mask ---------------------------------------------------------------------- */
+
+/* Replaces the mask output of gpu_dropout_forward (reference cuda/gpu_ops.cuh:126-127,
+ * cuda/gpu_ops.cu:712-734) for flat elements first .. first+n-1: mask[i] = 0 if dropped, 1 if
+ * kept. The reference's seed is a process counter (cuda/gpu_ops.cu:704,732); here it is an
+ * argument. */
+int dadattn_dropout_mask(uint8_t* mask, int64_t n, float rate, uint64_t seed, uint64_t offset,
+                         int64_t first, dadattn_stream_t stream);
+
+/* ---- bf16 tensor-core path (tcgen05 / TMEM / TMA) ---------------------------------------- */
+
+/* Head sizes the bf16 kernels cover (64, 128). */
+int dadattn_flash_bf16_supported(int d_head);
+
+/* bf16 form of gpu_flash_attention_forward (reference cuda/attention.cu:234-239 is the fp32
+ * original): q,k,v,out bf16 [BH,S,D], fp32 softmax and accumulation, lse fp32 [BH,S] in the
+ * reference's convention (natural log, scaled scores). Dropout arguments as above. All tensor
+ * pointers must be 16-byte aligned. */
+int dadattn_flash_fwd_bf16(uint16_t* out, float* lse, const uint16_t* q, const uint16_t* k,
+                           const uint16_t* v, int BH, int S, int D, float scale, float rate,
+                           uint64_t seed, uint64_t offset, int64_t unit0,
+                           dadattn_stream_t stream);
+
+/* bf16 form of gpu_flash_attention_backward (reference cuda/attention.cu:241-252). dq,dk,dv bf16,
+ * written not accumulated. workspace: caller-owned scratch of at least
+ * dadattn_flash_bwd_bf16_workspace_bytes(BH,S,D) bytes, 256-byte aligned (it holds delta and an
+ * fp32 dQ accumulator; contents are overwritten). */
+size_t dadattn_flash_bwd_bf16_workspace_bytes(int BH, int S, int D);
+int dadattn_flash_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspace,
+                           size_t workspace_bytes, const uint16_t* dout, const uint16_t* out,
+                           const float* lse, const uint16_t* q, const uint16_t* k,
+                           const uint16_t* v, int BH, int S, int D, float scale, float rate,
+                           uint64_t seed, uint64_t offset, int64_t unit0,
+                           dadattn_stream_t stream);
+
+/* ---- KV-cache decode --------------------------------------------------------------------- */
+
+/* Decode attention of model_forward_cached for ONE sequence on the reference's own cache
+ * (reference src/model.cpp:745-790; struct KVCache src/model.hpp:140-152): appends k_new,v_new
+ * [H*D] at row `pos` of k_cache,v_cache [H,max_len,D] fp32, then out[h] =
+ * softmax(q_h K_h[0..pos]^T * scale) V_h[0..pos]. Returns DADATTN_E_ARG when pos is outside
+ * [0, max_len) (the reference throws std::out_of_range, src/model.cpp:693-696). */
+int dadattn_decode_f32(float* out, const float* q, const float* k_new, const float* v_new,
+                       float* k_cache, float* v_cache, int H, int max_len, int D, int pos,
+                       float scale, dadattn_stream_t stream);
+
+/* Batched bf16 decode for many concurrent sequences (no counterpart signature in the reference,
+ * which decodes one fp32 sequence at a time; the arithmetic is that of src/model.cpp:758-790).
+ * Caches: [B,H,max_len,D] bf16. lengths[B] (int32, device) holds each sequence's current length
+ * L_b; the call writes k_new,v_new [B,H,D] at row L_b, attends over rows 0..L_b, and stores
+ * L_b + 1 back. Sequences with L_b >= max_len are left untouched and reported through
+ * DADATTN_E_ARG at the next dadattn_device_status(). workspace: split-K partials, at least
+ * dadattn_decode_workspace_bytes() bytes, 256-byte aligned. */
+size_t dadattn_decode_workspace_bytes(int B, int H, int D, int max_len);
+int dadattn_decode_bf16(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
+                        const uint16_t* v_new, uint16_t* k_cache, uint16_t* v_cache,
+                        int32_t* lengths, int B, int H, int D, int max_len, float scale,
+                        void* workspace, size_t workspace_bytes, dadattn_stream_t stream);
+
+/* Synchronises the stream and returns the sticky device-side status word of this device
+ * (0, or a DADATTN_E_* code recorded by a kernel: a bounded wait that ran out, a sequence at
+ * max_len). Clears the word. */
+int dadattn_device_status(dadattn_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DADATTN_H_ */

@@ -1,0 +1,96 @@
+"""GPU parity of the KV-cache decode kernels against the CPU oracle and the golden fixture."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import dadgpt_b200 as dad
+from dadgpt_b200.attention import device_status
+from tests.gpu_util import dev_f32, max_abs
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def test_decode_f32_against_golden(cuda):
+    g = np.load(os.path.join(GOLD, "decode_H4_L48_D32.npz"))
+    rng = np.random.default_rng(int(g["seed"]))
+    kc, vc = (rng.standard_normal((4, 48, 32), dtype=np.float32) for _ in range(2))
+    qs = rng.standard_normal((3, 4, 32), dtype=np.float32)
+    for i, n in enumerate(g["lens"]):
+        pos = int(n) - 1
+        tk, tv = dev_f32(kc, cuda), dev_f32(vc, cuda)
+        k_new, v_new = tk[:, pos].contiguous(), tv[:, pos].contiguous()
+        tk[:, pos] = 0  # the call itself must append the token's k, v
+        tv[:, pos] = 0
+        out = torch.empty(4, 32, device=cuda)
+        dad.decode_attention_f32(out, dev_f32(qs[i], cuda), k_new, v_new, tk, tv, pos, 32 ** -0.5)
+        assert max_abs(out.cpu().numpy(), g["out"][i]) <= 1e-5
+        assert torch.equal(tk, dev_f32(kc, cuda)) and torch.equal(tv, dev_f32(vc, cuda))
+
+
+@pytest.mark.parametrize("D", [16, 64, 128])
+def test_incremental_decode_equals_full_causal_forward(cuda, D):
+    # the relation pinned by the reference's KVCacheMatchesFullForward (tests/test_model.cpp:216-252),
+    # including the last slot of the context
+    H, S = 3, 37
+    q, k, v = (torch.randn(H, S, D, device=cuda) for _ in range(3))
+    full, lse = torch.empty_like(q), torch.empty(H, S, device=cuda)
+    scale = D ** -0.5
+    dad.gpu_flash_attention_forward(full, lse, q, k, v, H, S, D, scale)
+    kc, vc = torch.zeros(H, S, D, device=cuda), torch.zeros(H, S, D, device=cuda)
+    for pos in range(S):
+        out = torch.empty(H, D, device=cuda)
+        dad.decode_attention_f32(out, q[:, pos].contiguous(), k[:, pos].contiguous(),
+                                 v[:, pos].contiguous(), kc, vc, pos, scale)
+        assert (out - full[:, pos]).abs().max().item() <= 1e-4  # the reference's own bar
+    assert torch.equal(kc, k) and torch.equal(vc, v)
+
+
+def test_decode_f32_rejects_positions_outside_the_cache(cuda):
+    # reference: std::out_of_range (src/model.cpp:693-696, tests/test_model.cpp:254-277)
+    kc = torch.zeros(2, 8, 16, device=cuda)
+    x = torch.zeros(2, 16, device=cuda)
+    for pos in (-1, 8, 100):
+        with pytest.raises(IndexError):
+            dad.decode_attention_f32(x, x, x, x, kc, kc.clone(), pos, 0.25)
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_batched_bf16_decode_against_oracle(cuda, oracle, D):
+    B, H, L = 7, 5, 700
+    cache = dad.KVCacheBF16(B, H, L, D, device=cuda)
+    cache.k.copy_(torch.randn(B, H, L, D, device=cuda))
+    cache.v.copy_(torch.randn(B, H, L, D, device=cuda))
+    lens = torch.tensor([0, 1, 127, 128, 129, 511, 699], dtype=torch.int32, device=cuda)
+    cache.lengths.copy_(lens)
+    scale = D ** -0.5
+    for step in range(2):
+        q, kn, vn = (torch.randn(B, H, D, device=cuda).to(torch.bfloat16) for _ in range(3))
+        out = torch.empty_like(q)
+        if step == 1:
+            cache.lengths[-1] = 5  # the full sequence is replaced so that step 2 stays in range
+        before = cache.lengths.clone()
+        dad.decode_attention_bf16(out, q, kn, vn, cache, scale)
+        torch.cuda.synchronize()
+        assert torch.equal(cache.lengths, before + 1)
+        for b in range(B):  # appended rows hold the new token
+            assert torch.equal(cache.k[b, :, int(before[b])], kn[b])
+            assert torch.equal(cache.v[b, :, int(before[b])], vn[b])
+        want = oracle.decode(q.float().cpu().numpy(), cache.k.float().cpu().numpy(),
+                             cache.v.float().cpu().numpy(), cache.lengths.cpu().numpy(), scale)
+        assert max_abs(out.float().cpu().numpy(), want) <= 2e-2
+    assert device_status() == 0
+
+
+def test_full_sequence_is_skipped_and_reported(cuda):
+    B, H, L, D = 2, 2, 16, 64
+    cache = dad.KVCacheBF16(B, H, L, D, device=cuda)
+    cache.lengths.copy_(torch.tensor([3, 16], dtype=torch.int32))
+    x = torch.randn(B, H, D, device=cuda).to(torch.bfloat16)
+    out = torch.zeros_like(x)
+    dad.decode_attention_bf16(out, x, x, x, cache, 0.125)
+    assert device_status() == -1          # DADATTN_E_ARG recorded by the kernel, no fault
+    assert cache.lengths.tolist() == [4, 16]
+    assert (out[1] == 0).all() and device_status() == 0
