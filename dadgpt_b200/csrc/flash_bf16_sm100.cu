@@ -1,7 +1,412 @@
-// placeholder until the tcgen05 kernels land (replaced in the next commit)
+// bf16 fused causal attention for sm_100a: TMA-staged tiles, tcgen05 MMAs accumulating in tensor
+// memory, a warp-specialised online-softmax pipeline. The arithmetic is that of the reference's
+// fused kernels (cuda/attention.cu) with bf16 operands and fp32 accumulation; the interface is
+// its gpu_flash_attention_forward / _backward with bf16 pointers (include/dadattn.h).
+//
+// Forward, one CTA per 128 query rows of one (batch, head):
+//   warp 0      TMA producer: Q once, then K/V tiles of 128 keys through a 2-stage ring
+//   warp 1      MMA issuer (one elected lane) and owner of the TMEM allocation:
+//               S = Q K^T (128x128, fp32 in TMEM), O += P V (128xD, fp32 in TMEM)
+//   warps 2-5   softmax: one thread per query row (= one TMEM lane). Reads its row of S with
+//               tcgen05.ld, keeps the running max / sum, writes P as bf16 into shared memory
+//               in the 128-byte-swizzled layout the MMA reads, rescales O in TMEM only when the
+//               row max grew by more than 2^8 (lazy rescale; the final O / l is exact).
+// S_{j+1} is issued as soon as the softmax warps have pulled S_j into registers, so the tensor
+// core works on the next tile while the exponentials of the current one are computed; at D = 64
+// two CTAs share an SM, which hides the rest.
+//
+// Every mbarrier wait is bounded (sm100_ptx.cuh). If one runs out, the CTA raises its abort
+// flag, everybody falls through to the common exit, TMEM is freed, and DADATTN_E_TIMEOUT is
+// left in the device status word.
+#include <cuda_bf16.h>
+
+#include <cfloat>
+
 #include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace dadattn {
+
+// ---------------------------------------------------------------------------------------------
+// Tensor maps (host)
+// ---------------------------------------------------------------------------------------------
+namespace {
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) !=
+            cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+}  // namespace
+
+int make_tensor_map_bf16(CUtensorMap* map, const void* base, int BH, int S, int D, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(DADATTN_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S),
+                              static_cast<cuuint64_t>(BH)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2,
+                                 static_cast<cuuint64_t>(S) * D * 2};
+  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(DADATTN_E_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return DADATTN_OK;
+}
+
+namespace {
+
+using namespace ptx;
+
+constexpr int kBM = 128;          // query rows per CTA
+constexpr int kBN = 128;          // keys per tile
+constexpr int kStages = 2;        // K/V ring depth
+constexpr int kPanelBytes = 128 * 128;  // [128 rows][64 bf16], 128-byte rows, swizzled
+constexpr int kFwdThreads = 192;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units: P stays below 2^8
+
+template <int D>
+struct FwdSmem {
+  static constexpr int kPanels = D / 64;
+  static constexpr int kQ = 0;
+  static constexpr int kK = kQ + kPanels * kPanelBytes;
+  static constexpr int kV = kK + kStages * kPanels * kPanelBytes;
+  static constexpr int kP = kV + kStages * kPanels * kPanelBytes;
+  static constexpr int kBars = kP + 2 * kPanelBytes;
+  static constexpr int kBytes = kBars + 256;
+};
+
+struct FwdBars {
+  uint64_t q_full, k_full[kStages], v_full[kStages], kv_empty[kStages];
+  uint64_t s_full, s_free, p_full, o_done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int D, bool DROP>
+__global__ void __launch_bounds__(kFwdThreads, D == 64 ? 2 : 1)
+flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
+                      const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                      float* __restrict__ lse, int S, float scale, float rate, PhiloxKey rng,
+                      int64_t unit0, int* __restrict__ status) {
+  using L = FwdSmem<D>;
+  constexpr int kPanels = L::kPanels;
+  constexpr uint32_t kTmemCols = 256;  // S: [0,128)  O: [128, 128 + D)
+  constexpr uint32_t kColS = 0, kColO = 128;
+
+  extern __shared__ __align__(1024) uint8_t smem[];
+  FwdBars* bars = reinterpret_cast<FwdBars*>(smem + L::kBars);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int qt = gridDim.x - 1 - blockIdx.x;  // heaviest tiles first
+  const int bh = blockIdx.y;
+  const int q0 = qt * kBM;
+  const int n_kv = qt + 1;  // causal: key tiles 0..qt
+
+  if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled layouts need a 1024-byte aligned base
+    if (threadIdx.x == 0) atomicExch(status, DADATTN_E_CUDA);
+    return;
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bars->k_full[s], 1);
+      mbar_init(&bars->v_full[s], 1);
+      mbar_init(&bars->kv_empty[s], 1);
+    }
+    mbar_init(&bars->s_full, 1);
+    mbar_init(&bars->s_free, 128);
+    mbar_init(&bars->p_full, 128);
+    mbar_init(&bars->o_done, 1);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (elect_one()) {
+      prefetch_tensormap(&map_q);
+      prefetch_tensormap(&map_k);
+      prefetch_tensormap(&map_v);
+      mbar_arrive_expect_tx(&bars->q_full, kPanels * kPanelBytes);
+      for (int p = 0; p < kPanels; ++p)
+        tma_load_3d(smem + L::kQ + p * kPanelBytes, &map_q, &bars->q_full, p * 64, q0, bh);
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j % kStages, use = j / kStages;
+        if (use > 0 && !mbar_wait(&bars->kv_empty[s], (use - 1) & 1, abort_flag)) break;
+        uint8_t* kdst = smem + L::kK + s * kPanels * kPanelBytes;
+        uint8_t* vdst = smem + L::kV + s * kPanels * kPanelBytes;
+        mbar_arrive_expect_tx(&bars->k_full[s], kPanels * kPanelBytes);
+        for (int p = 0; p < kPanels; ++p)
+          tma_load_3d(kdst + p * kPanelBytes, &map_k, &bars->k_full[s], p * 64, j * kBN, bh);
+        mbar_arrive_expect_tx(&bars->v_full[s], kPanels * kPanelBytes);
+        for (int p = 0; p < kPanels; ++p)
+          tma_load_3d(vdst + p * kPanelBytes, &map_v, &bars->v_full[s], p * 64, j * kBN, bh);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (elect_one()) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(kBM, kBN, 0, 0);  // Q, K: K-major
+      constexpr uint32_t idesc_o = make_idesc_bf16(kBM, 64, 0, 1);   // P K-major, V MN-major
+      const uint32_t q_addr = smem_u32(smem + L::kQ);
+      const uint32_t p_addr = smem_u32(smem + L::kP);
+      bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
+
+      // O[:, 64 pn .. 64 pn + 63] (+)= P_i V_i for tile i
+      auto issue_pv = [&](int i) -> bool {
+        const int s = i % kStages;
+        if (!mbar_wait(&bars->v_full[s], (i / kStages) & 1, abort_flag)) return false;
+        if (!mbar_wait(&bars->p_full, i & 1, abort_flag)) return false;
+        tc_fence_after_sync();
+        const uint32_t v_addr = smem_u32(smem + L::kV + s * kPanels * kPanelBytes);
+#pragma unroll
+        for (int pn = 0; pn < kPanels; ++pn) {
+#pragma unroll
+          for (int kk = 0; kk < kBN / 16; ++kk) {
+            const uint64_t a = make_smem_desc_sw128(p_addr + (kk / 4) * kPanelBytes + (kk % 4) * 32, 0);
+            const uint64_t b = make_smem_desc_sw128(v_addr + pn * kPanelBytes + kk * 2048, kPanelBytes);
+            mma_ss(tmem + kColO + pn * 64, a, b, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+          }
+        }
+        mma_commit(&bars->kv_empty[s]);
+        mma_commit(&bars->o_done);
+        return true;
+      };
+
+      for (int j = 0; ok && j < n_kv; ++j) {
+        const int s = j % kStages;
+        ok = mbar_wait(&bars->k_full[s], (j / kStages) & 1, abort_flag);
+        if (ok && j > 0) ok = mbar_wait(&bars->s_free, (j - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t k_addr = smem_u32(smem + L::kK + s * kPanels * kPanelBytes);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * kPanelBytes + (kk % 4) * 32;
+          mma_ss(tmem + kColS, make_smem_desc_sw128(q_addr + off, 0),
+                 make_smem_desc_sw128(k_addr + off, 0), idesc_s, kk > 0 ? 1u : 0u);
+        }
+        mma_commit(&bars->s_full);
+        if (j > 0) ok = issue_pv(j - 1);
+      }
+      if (ok) issue_pv(n_kv - 1);
+    }
+  } else {
+    // ------------------------------ softmax ------------------------------
+    const int quad = warp % 4;            // TMEM lane quadrant this warp may touch
+    const int row = quad * 32 + lane;     // row within the tile = TMEM lane
+    const int r = q0 + row;               // query index
+    const uint32_t tlane = tmem + (static_cast<uint32_t>(quad * 32) << 16);
+    const float scale_log2 = scale * kLog2e;
+    const float keep_scale = DROP ? 1.0f / (1.0f - rate) : 1.0f;
+    uint8_t* p_row = smem + L::kP + row * 128;
+    float m = -FLT_MAX, l = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < n_kv; ++j) {
+      if (!(ok = mbar_wait(&bars->s_full, j & 1, abort_flag))) break;
+      tc_fence_after_sync();
+      float t[kBN];
+#pragma unroll
+      for (int c = 0; c < kBN / 32; ++c)
+        tmem_ld32(tlane + kColS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&t[c * 32]));
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      mbar_arrive(&bars->s_free);  // S is in registers: the next QK^T may overwrite it
+
+      const int c0 = j * kBN;
+      float mx = -FLT_MAX;
+      if (j == n_kv - 1) {  // the diagonal tile is the only one that needs the causal mask
+#pragma unroll
+        for (int c = 0; c < kBN; ++c) {
+          t[c] = (c0 + c <= r) ? t[c] * scale_log2 : -INFINITY;
+          mx = fmaxf(mx, t[c]);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < kBN; ++c) {
+          t[c] *= scale_log2;
+          mx = fmaxf(mx, t[c]);
+        }
+      }
+
+      bool waited_o = false;
+      if (j == 0) {
+        m = mx;  // O is first written by an MMA with accumulate = 0: nothing to rescale
+      } else if (__any_sync(0xffffffffu, mx > m + kRescaleThreshold)) {
+        if (!(ok = mbar_wait(&bars->o_done, (j - 1) & 1, abort_flag))) break;
+        waited_o = true;
+        tc_fence_after_sync();
+        const float m_new = fmaxf(m, mx);
+        const float corr = ex2(m - m_new);
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(tlane + kColO + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+          tmem_st32(tlane + kColO + c * 32, o);
+        }
+        tmem_wait_st();
+        l *= corr;
+        m = m_new;
+      }
+
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < kBN; ++c) {
+        t[c] = ex2(t[c] - m);
+        sum += t[c];
+      }
+      l += sum;
+      if (DROP) {
+        const uint64_t idx0 = (static_cast<uint64_t>(unit0 + bh) * S + r) * S + c0;
+#pragma unroll 4
+        for (int c = 0; c < kBN; ++c)
+          t[c] = (t[c] != 0.f && philox_keep(rng, idx0 + c, rate)) ? t[c] * keep_scale : 0.f;
+      }
+
+      // P_{j-1} must have been consumed by its MMA before the buffer is overwritten
+      if (j > 0 && !waited_o && !(ok = mbar_wait(&bars->o_done, (j - 1) & 1, abort_flag))) break;
+#pragma unroll
+      for (int ch = 0; ch < kBN / 8; ++ch) {
+        uint4 w;
+        w.x = pack_bf16(t[ch * 8 + 0], t[ch * 8 + 1]);
+        w.y = pack_bf16(t[ch * 8 + 2], t[ch * 8 + 3]);
+        w.z = pack_bf16(t[ch * 8 + 4], t[ch * 8 + 5]);
+        w.w = pack_bf16(t[ch * 8 + 6], t[ch * 8 + 7]);
+        const int panel = ch / 8, cc = ch % 8;
+        *reinterpret_cast<uint4*>(p_row + panel * kPanelBytes + ((cc ^ (row & 7)) << 4)) = w;
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&bars->p_full);
+    }
+
+    // Epilogue: O / l -> bf16, lse in natural-log units of the scaled scores
+    if (ok && (ok = mbar_wait(&bars->o_done, (n_kv - 1) & 1, abort_flag))) {
+      tc_fence_after_sync();
+      const float inv = 1.0f / l;
+      __nv_bfloat16* dst = out + (static_cast<size_t>(bh) * S + r) * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tlane + kColO + c * 32, o);
+        tmem_wait_ld();
+        if (r < S) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 w;
+            w.x = pack_bf16(__uint_as_float(o[8 * i + 0]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
+            w.y = pack_bf16(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
+            w.z = pack_bf16(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
+            w.w = pack_bf16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + i * 8) = w;
+          }
+        }
+      }
+      if (r < S) lse[static_cast<size_t>(bh) * S + r] = (m + log2f(l)) * kLn2;
+    }
+  }
+
+  // ------------------------------ common exit ------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+  if (threadIdx.x == 0 && bars->abort_flag) atomicExch(status, DADATTN_E_TIMEOUT);
+}
+
+template <int D, bool DROP>
+int launch_fwd_bf16(uint16_t* out, float* lse, const uint16_t* q, const uint16_t* k,
+                    const uint16_t* v, int BH, int S, float scale, float rate, uint64_t seed,
+                    uint64_t offset, int64_t unit0, cudaStream_t st) {
+  CUtensorMap mq, mk, mv;
+  if (int rc = make_tensor_map_bf16(&mq, q, BH, S, D, kBM)) return rc;
+  if (int rc = make_tensor_map_bf16(&mk, k, BH, S, D, kBN)) return rc;
+  if (int rc = make_tensor_map_bf16(&mv, v, BH, S, D, kBN)) return rc;
+  int* status = device_status_word();
+  if (!status) return DADATTN_E_CUDA;
+  auto kern = flash_fwd_bf16_kernel<D, DROP>;
+  DAD_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                FwdSmem<D>::kBytes));
+  dim3 grid((S + kBM - 1) / kBM, BH);
+  kern<<<grid, kFwdThreads, FwdSmem<D>::kBytes, st>>>(
+      mq, mk, mv, reinterpret_cast<__nv_bfloat16*>(out), lse, S, scale, rate,
+      make_philox(seed, offset), unit0, status);
+  DAD_LAUNCH_CHECK("flash_fwd_bf16_kernel");
+  return DADATTN_OK;
+}
+
+}  // namespace
+}  // namespace dadattn
+
 using namespace dadattn;
-extern "C" int dadattn_flash_bf16_supported(int d) { return d == 64 || d == 128; }
-extern "C" int dadattn_flash_fwd_bf16(uint16_t*, float*, const uint16_t*, const uint16_t*, const uint16_t*, int, int, int, float, float, uint64_t, uint64_t, int64_t, dadattn_stream_t) { return fail(DADATTN_E_UNSUPPORTED, "bf16 forward not built"); }
-extern "C" size_t dadattn_flash_bwd_bf16_workspace_bytes(int BH, int S, int D) { return (size_t)BH * S * (D + 1) * 4; }
-extern "C" int dadattn_flash_bwd_bf16(uint16_t*, uint16_t*, uint16_t*, void*, size_t, const uint16_t*, const uint16_t*, const float*, const uint16_t*, const uint16_t*, const uint16_t*, int, int, int, float, float, uint64_t, uint64_t, int64_t, dadattn_stream_t) { return fail(DADATTN_E_UNSUPPORTED, "bf16 backward not built"); }
+
+extern "C" int dadattn_flash_bf16_supported(int d_head) { return d_head == 64 || d_head == 128; }
+
+extern "C" int dadattn_flash_fwd_bf16(uint16_t* out, float* lse, const uint16_t* q,
+                                      const uint16_t* k, const uint16_t* v, int BH, int S, int D,
+                                      float scale, float rate, uint64_t seed, uint64_t offset,
+                                      int64_t unit0, dadattn_stream_t stream) {
+  if (!out || !lse || !q || !k || !v) return fail(DADATTN_E_ARG, "null tensor pointer");
+  if (BH <= 0 || S <= 0) return fail(DADATTN_E_ARG, "BH=%d and S=%d must be positive", BH, S);
+  if (BH > 65535) return fail(DADATTN_E_UNSUPPORTED, "BH=%d exceeds 65535 per call", BH);
+  if (!dadattn_flash_bf16_supported(D))
+    return fail(DADATTN_E_UNSUPPORTED, "flash attention bf16: unsupported d_head %d", D);
+  if (!(rate >= 0.0f && rate < 1.0f))
+    return fail(DADATTN_E_ARG, "dropout rate %f outside [0,1)", static_cast<double>(rate));
+  if (!aligned(out, 16) || !aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) ||
+      !aligned(lse, 4))
+    return fail(DADATTN_E_ARG, "bf16 tensors must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool drop = rate > 0.f;
+  if (D == 64)
+    return drop ? launch_fwd_bf16<64, true>(out, lse, q, k, v, BH, S, scale, rate, seed, offset, unit0, st)
+                : launch_fwd_bf16<64, false>(out, lse, q, k, v, BH, S, scale, 0.f, 0, 0, 0, st);
+  return drop ? launch_fwd_bf16<128, true>(out, lse, q, k, v, BH, S, scale, rate, seed, offset, unit0, st)
+              : launch_fwd_bf16<128, false>(out, lse, q, k, v, BH, S, scale, 0.f, 0, 0, 0, st);
+}
+
+extern "C" size_t dadattn_flash_bwd_bf16_workspace_bytes(int BH, int S, int D) {
+  if (BH <= 0 || S <= 0 || D <= 0) return 0;
+  return static_cast<size_t>(BH) * S * (D + 1) * sizeof(float);
+}
+
+extern "C" int dadattn_flash_bwd_bf16(uint16_t*, uint16_t*, uint16_t*, void*, size_t,
+                                      const uint16_t*, const uint16_t*, const float*,
+                                      const uint16_t*, const uint16_t*, const uint16_t*, int, int,
+                                      int, float, float, uint64_t, uint64_t, int64_t,
+                                      dadattn_stream_t) {
+  return fail(DADATTN_E_UNSUPPORTED, "bf16 backward is not implemented yet");
+}
