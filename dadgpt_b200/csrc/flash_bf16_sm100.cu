@@ -397,16 +397,3 @@ extern "C" int dadattn_flash_fwd_bf16(uint16_t* out, float* lse, const uint16_t*
   return drop ? launch_fwd_bf16<128, true>(out, lse, q, k, v, BH, S, scale, rate, seed, offset, unit0, st)
               : launch_fwd_bf16<128, false>(out, lse, q, k, v, BH, S, scale, 0.f, 0, 0, 0, st);
 }
-
-extern "C" size_t dadattn_flash_bwd_bf16_workspace_bytes(int BH, int S, int D) {
-  if (BH <= 0 || S <= 0 || D <= 0) return 0;
-  return static_cast<size_t>(BH) * S * (D + 1) * sizeof(float);
-}
-
-extern "C" int dadattn_flash_bwd_bf16(uint16_t*, uint16_t*, uint16_t*, void*, size_t,
-                                      const uint16_t*, const uint16_t*, const float*,
-                                      const uint16_t*, const uint16_t*, const uint16_t*, int, int,
-                                      int, float, float, uint64_t, uint64_t, int64_t,
-                                      dadattn_stream_t) {
-  return fail(DADATTN_E_UNSUPPORTED, "bf16 backward is not implemented yet");
-}

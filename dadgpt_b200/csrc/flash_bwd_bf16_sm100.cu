@@ -1,0 +1,455 @@
+// bf16 fused causal attention backward for sm_100a (tcgen05 / TMEM / TMA).
+//
+// Same decomposition as the reference's backward (cuda/attention.cu:215-228): a delta pre-pass,
+// one kernel that owns key tiles and produces dK/dV, one that owns query tiles and produces dQ.
+// Nothing is accumulated across CTAs, so there are no atomics and results are deterministic,
+// as in the reference. Both tensor-core kernels are one template:
+//
+//   resident tiles R1,R2 (128 rows)   streamed tiles C1,C2 (128 rows each step)
+//   dK/dV kernel:  K, V               Q, dO      rows of the score tile = keys
+//   dQ    kernel:  Q, dO              K, V       rows of the score tile = queries
+//
+//   X1 = R1 C1^T  (S or S^T)          X2 = R2 C2^T  (dP or dP^T)        -> TMEM, fp32
+//   p  = exp2(X1 * scale * log2e - lse[query] * log2e)
+//   ds = p * (X2 * dropmask/(1-rate) - delta[query]) * scale
+//   dK/dV kernel:  dV += (p*dropmask/(1-rate))^T-tile . C2,  dK += ds-tile . C1
+//   dQ    kernel:  dQ += ds-tile . C1
+//
+// p and ds are written by the compute warps as bf16 into shared memory in the 128-byte
+// swizzled K-major layout and consumed as the A operand; the streamed tiles serve as the
+// MN-major B operand of the accumulating MMAs, straight from where TMA put them.
+//   warp 0      TMA producer          warp 1      MMA issuer + TMEM owner
+//   warps 2-9   compute: two warps per TMEM lane quadrant, each taking 64 of the 128 columns
+#include <cuda_bf16.h>
+
+#include <cfloat>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace dadattn {
+namespace {
+
+using namespace ptx;
+
+constexpr int kTileRows = 128;
+constexpr int kPanelBytes = 128 * 128;
+constexpr int kBwdThreads = 320;
+constexpr int kComputeThreads = 256;
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int D>
+struct BwdSmem {
+  static constexpr int kPanels = D / 64;
+  static constexpr int kStages = D == 64 ? 2 : 1;
+  static constexpr int kTile = kPanels * kPanelBytes;     // one [128, D] bf16 tile
+  static constexpr int kR1 = 0;
+  static constexpr int kR2 = kR1 + kTile;
+  static constexpr int kC1 = kR2 + kTile;
+  static constexpr int kC2 = kC1 + kStages * kTile;
+  static constexpr int kP = kC2 + kStages * kTile;        // [128][128] bf16, two panels
+  static constexpr int kDS = kP + 2 * kPanelBytes;
+  static constexpr int kVec = kDS + 2 * kPanelBytes;      // lse*log2e and delta: [2][2][128] fp32
+  static constexpr int kBars = kVec + 2 * 2 * 128 * 4;
+  static constexpr int kBytes = kBars + 256;
+};
+
+struct BwdBars {
+  uint64_t r_full, c1_full[2], c2_full[2], c_empty[2];
+  uint64_t x_full, x_free, w_full, acc_done, vec_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// delta[r] = sum_d dO[r,d] * O[r,d]; 8 bf16 per lane, D/8 lanes per row.
+template <int D>
+__global__ void flash_delta_bf16_kernel(float* __restrict__ delta,
+                                        const __nv_bfloat16* __restrict__ dout,
+                                        const __nv_bfloat16* __restrict__ out, int64_t rows) {
+  constexpr int L = D / 8;
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t r = t / L;
+  const int c = static_cast<int>(t % L) * 8;
+  float sum = 0.f;
+  if (r < rows) {
+    const uint4 a = *reinterpret_cast<const uint4*>(dout + r * D + c);
+    const uint4 b = *reinterpret_cast<const uint4*>(out + r * D + c);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      sum = fmaf(__uint_as_float(aw[i] << 16), __uint_as_float(bw[i] << 16), sum);
+      sum = fmaf(__uint_as_float(aw[i] & 0xffff0000u), __uint_as_float(bw[i] & 0xffff0000u), sum);
+    }
+  }
+#pragma unroll
+  for (int o = L / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (r < rows && c == 0) delta[r] = sum;
+}
+
+// KV = true: dK/dV kernel (grid.x = key tile). KV = false: dQ kernel (grid.x = query tile).
+template <int D, bool KV, bool DROP>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
+                      const __grid_constant__ CUtensorMap map_r2,
+                      const __grid_constant__ CUtensorMap map_c1,
+                      const __grid_constant__ CUtensorMap map_c2,
+                      __nv_bfloat16* __restrict__ out1, __nv_bfloat16* __restrict__ out2,
+                      const float* __restrict__ lse, const float* __restrict__ delta, int S,
+                      float scale, float rate, PhiloxKey rng, int64_t unit0,
+                      int* __restrict__ status) {
+  using L = BwdSmem<D>;
+  constexpr int kPanels = L::kPanels;
+  constexpr int kStages = L::kStages;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kColX1 = 0, kColX2 = 128, kColA1 = 256, kColA2 = 256 + D;
+
+  extern __shared__ __align__(1024) uint8_t smem[];
+  BwdBars* bars = reinterpret_cast<BwdBars*>(smem + L::kBars);
+  volatile int* abort_flag = &bars->abort_flag;
+  float* vec = reinterpret_cast<float*>(smem + L::kVec);
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int n_tiles = (S + kTileRows - 1) / kTileRows;
+  const int bh = blockIdx.y;
+  // dK/dV: key tile kt streams query tiles kt..n-1 (low kt = most work = scheduled first).
+  // dQ:    query tile qt streams key tiles 0..qt   (high qt first).
+  const int own = KV ? static_cast<int>(blockIdx.x) : n_tiles - 1 - static_cast<int>(blockIdx.x);
+  const int first = KV ? own : 0;
+  const int n_it = KV ? n_tiles - own : own + 1;
+  const int row0 = own * kTileRows;
+
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicExch(status, DADATTN_E_CUDA);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->r_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->c1_full[s], 1);
+      mbar_init(&bars->c2_full[s], 1);
+      mbar_init(&bars->c_empty[s], 1);
+    }
+    mbar_init(&bars->x_full, 1);
+    mbar_init(&bars->x_free, kComputeThreads);
+    mbar_init(&bars->w_full, kComputeThreads);
+    mbar_init(&bars->acc_done, 1);
+    mbar_init(&bars->vec_full, kComputeThreads);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (elect_one()) {
+      prefetch_tensormap(&map_r1);
+      prefetch_tensormap(&map_r2);
+      prefetch_tensormap(&map_c1);
+      prefetch_tensormap(&map_c2);
+      mbar_arrive_expect_tx(&bars->r_full, 2 * L::kTile);
+      for (int p = 0; p < kPanels; ++p) {
+        tma_load_3d(smem + L::kR1 + p * kPanelBytes, &map_r1, &bars->r_full, p * 64, row0, bh);
+        tma_load_3d(smem + L::kR2 + p * kPanelBytes, &map_r2, &bars->r_full, p * 64, row0, bh);
+      }
+      for (int i = 0; i < n_it; ++i) {
+        const int s = i % kStages, use = i / kStages;
+        if (use > 0 && !mbar_wait(&bars->c_empty[s], (use - 1) & 1, abort_flag)) break;
+        const int c_row0 = (first + i) * kTileRows;
+        mbar_arrive_expect_tx(&bars->c1_full[s], L::kTile);
+        for (int p = 0; p < kPanels; ++p)
+          tma_load_3d(smem + L::kC1 + s * L::kTile + p * kPanelBytes, &map_c1, &bars->c1_full[s],
+                      p * 64, c_row0, bh);
+        mbar_arrive_expect_tx(&bars->c2_full[s], L::kTile);
+        for (int p = 0; p < kPanels; ++p)
+          tma_load_3d(smem + L::kC2 + s * L::kTile + p * kPanelBytes, &map_c2, &bars->c2_full[s],
+                      p * 64, c_row0, bh);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (elect_one()) {
+      constexpr uint32_t idesc_x = make_idesc_bf16(128, 128, 0, 0);  // both operands K-major
+      constexpr uint32_t idesc_a = make_idesc_bf16(128, 64, 0, 1);   // B = streamed tile, MN-major
+      const uint32_t r1 = smem_u32(smem + L::kR1), r2 = smem_u32(smem + L::kR2);
+      const uint32_t p_addr = smem_u32(smem + L::kP), ds_addr = smem_u32(smem + L::kDS);
+      bool ok = mbar_wait(&bars->r_full, 0, abort_flag);
+      for (int i = 0; ok && i < n_it; ++i) {
+        const int s = i % kStages;
+        const uint32_t par = (i / kStages) & 1;
+        const uint32_t c1 = smem_u32(smem + L::kC1 + s * L::kTile);
+        const uint32_t c2 = smem_u32(smem + L::kC2 + s * L::kTile);
+        if (!(ok = mbar_wait(&bars->c1_full[s], par, abort_flag))) break;
+        if (i > 0 && !(ok = mbar_wait(&bars->x_free, (i - 1) & 1, abort_flag))) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * kPanelBytes + (kk % 4) * 32;
+          mma_ss(tmem + kColX1, make_smem_desc_sw128(r1 + off, 0),
+                 make_smem_desc_sw128(c1 + off, 0), idesc_x, kk > 0 ? 1u : 0u);
+        }
+        if (!(ok = mbar_wait(&bars->c2_full[s], par, abort_flag))) break;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * kPanelBytes + (kk % 4) * 32;
+          mma_ss(tmem + kColX2, make_smem_desc_sw128(r2 + off, 0),
+                 make_smem_desc_sw128(c2 + off, 0), idesc_x, kk > 0 ? 1u : 0u);
+        }
+        mma_commit(&bars->x_full);
+
+        if (!(ok = mbar_wait(&bars->w_full, i & 1, abort_flag))) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int pn = 0; pn < kPanels; ++pn) {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t a_off = (kk / 4) * kPanelBytes + (kk % 4) * 32;
+            const uint32_t b_off = pn * kPanelBytes + kk * 2048;
+            const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
+            if (KV) {
+              mma_ss(tmem + kColA1 + pn * 64, make_smem_desc_sw128(p_addr + a_off, 0),
+                     make_smem_desc_sw128(c2 + b_off, kPanelBytes), idesc_a, acc);
+            }
+            mma_ss(tmem + (KV ? kColA2 : kColA1) + pn * 64, make_smem_desc_sw128(ds_addr + a_off, 0),
+                   make_smem_desc_sw128(c1 + b_off, kPanelBytes), idesc_a, acc);
+          }
+        }
+        mma_commit(&bars->c_empty[s]);
+        mma_commit(&bars->acc_done);
+      }
+    }
+  } else {
+    // ------------------------------ compute warps ------------------------------
+    const int cw = warp - 2;              // 0..7
+    const int quad = warp % 4;            // TMEM lane quadrant of this warp
+    const int half = cw / 4;              // which 64 columns of the 128
+    const int ct = cw * 32 + lane;        // 0..255 among the compute threads
+    const int row = quad * 32 + lane;     // row of the score tile = TMEM lane
+    const int grow = row0 + row;          // key (KV) or query (dQ) index of this row
+    const uint32_t tlane = tmem + (static_cast<uint32_t>(quad * 32) << 16);
+    const float scale_log2 = scale * kLog2e;
+    const float keep_scale = DROP ? 1.0f / (1.0f - rate) : 1.0f;
+    const size_t vec_base = static_cast<size_t>(bh) * S;
+    uint8_t* p_row = smem + L::kP + row * 128;
+    uint8_t* ds_row = smem + L::kDS + row * 128;
+    float row_lse2 = 0.f, row_delta = 0.f;
+    if (!KV) {  // per-row scalars; rows beyond S contribute nothing (p = exp2(-inf) = 0)
+      row_lse2 = grow < S ? lse[vec_base + grow] * kLog2e : INFINITY;
+      row_delta = grow < S ? delta[vec_base + grow] : 0.f;
+    }
+    bool ok = true;
+
+    for (int i = 0; i < n_it; ++i) {
+      const int col0 = (first + i) * kTileRows;  // first query (KV) / key (dQ) of the streamed tile
+      const bool diagonal = KV ? (i == 0) : (i == n_it - 1);
+      float* v_lse = vec + (i & 1) * 256;
+      float* v_delta = v_lse + 128;
+      if (KV) {  // per-column vectors of this query tile
+        const int q = col0 + (ct & 127);
+        if (ct < 128) v_lse[ct] = q < S ? lse[vec_base + q] * kLog2e : INFINITY;
+        else v_delta[ct - 128] = q < S ? delta[vec_base + q] : 0.f;
+        // an mbarrier rather than a named barrier: its wait is bounded like every other one
+        mbar_arrive(&bars->vec_full);
+        if (!(ok = mbar_wait(&bars->vec_full, i & 1, abort_flag))) break;
+      }
+      if (!(ok = mbar_wait(&bars->x_full, i & 1, abort_flag))) break;
+      tc_fence_after_sync();
+      // the previous step's p / ds tiles must have been consumed before they are overwritten
+      if (i > 0 && !(ok = mbar_wait(&bars->acc_done, (i - 1) & 1, abort_flag))) break;
+
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        const int cbase = half * 64 + ch * 32;  // column within the tile
+        uint32_t x1[32], x2[32];
+        tmem_ld32(tlane + kColX1 + cbase, x1);
+        tmem_ld32(tlane + kColX2 + cbase, x2);
+        tmem_wait_ld();
+        uint32_t pw[16], dw[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = cbase + c + e;
+            const int gcol = col0 + col;
+            const int key = KV ? grow : gcol, query = KV ? gcol : grow;
+            const float l2 = KV ? v_lse[col] : row_lse2;
+            const float dl = KV ? v_delta[col] : row_delta;
+            float p = ex2(fmaf(__uint_as_float(x1[c + e]), scale_log2, -l2));
+            if (diagonal && key > query) p = 0.f;
+            float g = __uint_as_float(x2[c + e]);
+            float pd = p;
+            if (DROP) {
+              const uint64_t idx = (static_cast<uint64_t>(unit0 + bh) * S + query) * S + key;
+              const float mk = (p != 0.f && philox_keep(rng, idx, rate)) ? keep_scale : 0.f;
+              pd = p * mk;
+              g *= mk;
+            }
+            pv[e] = pd;
+            dv[e] = p * (g - dl) * scale;
+          }
+          pw[c / 2] = pack_bf16(pv[0], pv[1]);
+          dw[c / 2] = pack_bf16(dv[0], dv[1]);
+        }
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) {
+          const int chunk = (ch * 32) / 8 + v4;  // 16-byte chunk within this half's panel
+          const int off = half * kPanelBytes + ((chunk ^ (row & 7)) << 4);
+          if (KV)
+            *reinterpret_cast<uint4*>(p_row + off) =
+                make_uint4(pw[4 * v4], pw[4 * v4 + 1], pw[4 * v4 + 2], pw[4 * v4 + 3]);
+          *reinterpret_cast<uint4*>(ds_row + off) =
+              make_uint4(dw[4 * v4], dw[4 * v4 + 1], dw[4 * v4 + 2], dw[4 * v4 + 3]);
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&bars->x_free);
+      fence_proxy_async_smem();
+      mbar_arrive(&bars->w_full);
+    }
+
+    // Epilogue. dK/dV kernel: half 0 stores dV, half 1 stores dK. dQ kernel: halves split D.
+    if (ok && (ok = mbar_wait(&bars->acc_done, (n_it - 1) & 1, abort_flag))) {
+      tc_fence_after_sync();
+      constexpr int kCols = KV ? D : D / 2;
+      const uint32_t col_base = KV ? (half == 0 ? kColA1 : kColA2) : kColA1 + half * (D / 2);
+      __nv_bfloat16* dst = (KV ? (half == 0 ? out1 : out2) : out1) +
+                           (static_cast<size_t>(bh) * S + grow) * D + (KV ? 0 : half * (D / 2));
+#pragma unroll
+      for (int c = 0; c < kCols / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tlane + col_base + c * 32, o);
+        tmem_wait_ld();
+        if (grow < S) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            *reinterpret_cast<uint4*>(dst + c * 32 + i * 8) = make_uint4(
+                pack_bf16(__uint_as_float(o[8 * i + 0]), __uint_as_float(o[8 * i + 1])),
+                pack_bf16(__uint_as_float(o[8 * i + 2]), __uint_as_float(o[8 * i + 3])),
+                pack_bf16(__uint_as_float(o[8 * i + 4]), __uint_as_float(o[8 * i + 5])),
+                pack_bf16(__uint_as_float(o[8 * i + 6]), __uint_as_float(o[8 * i + 7])));
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+  if (threadIdx.x == 0 && bars->abort_flag) atomicExch(status, DADATTN_E_TIMEOUT);
+}
+
+thread_local cudaEvent_t* g_stage_events = nullptr;
+thread_local int g_stage_event_count = 0;
+
+inline void stage_event(int i, cudaStream_t st) {
+  if (g_stage_events && i < g_stage_event_count) cudaEventRecord(g_stage_events[i], st);
+}
+
+template <int D, bool DROP>
+int launch_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, float* delta, const uint16_t* dout,
+                    const uint16_t* out, const float* lse, const uint16_t* q, const uint16_t* k,
+                    const uint16_t* v, int BH, int S, float scale, float rate, uint64_t seed,
+                    uint64_t offset, int64_t unit0, cudaStream_t st) {
+  CUtensorMap mq, mk, mv, mdo;
+  if (int rc = make_tensor_map_bf16(&mq, q, BH, S, D, kTileRows)) return rc;
+  if (int rc = make_tensor_map_bf16(&mk, k, BH, S, D, kTileRows)) return rc;
+  if (int rc = make_tensor_map_bf16(&mv, v, BH, S, D, kTileRows)) return rc;
+  if (int rc = make_tensor_map_bf16(&mdo, dout, BH, S, D, kTileRows)) return rc;
+  int* status = device_status_word();
+  if (!status) return DADATTN_E_CUDA;
+  using BF = __nv_bfloat16;
+
+  stage_event(0, st);
+  const int64_t rows = static_cast<int64_t>(BH) * S;
+  const int64_t threads = rows * (D / 8);
+  flash_delta_bf16_kernel<D><<<static_cast<unsigned>((threads + 255) / 256), 256, 0, st>>>(
+      delta, reinterpret_cast<const BF*>(dout), reinterpret_cast<const BF*>(out), rows);
+  DAD_LAUNCH_CHECK("flash_delta_bf16_kernel");
+  stage_event(1, st);
+
+  const PhiloxKey rng = make_philox(seed, offset);
+  dim3 grid((S + kTileRows - 1) / kTileRows, BH);
+  auto kkv = flash_bwd_bf16_kernel<D, true, DROP>;
+  DAD_CUDA(cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                BwdSmem<D>::kBytes));
+  kkv<<<grid, kBwdThreads, BwdSmem<D>::kBytes, st>>>(mk, mv, mq, mdo, reinterpret_cast<BF*>(dv),
+                                                    reinterpret_cast<BF*>(dk), lse, delta, S,
+                                                    scale, rate, rng, unit0, status);
+  DAD_LAUNCH_CHECK("flash_bwd_bf16_kernel<dkdv>");
+  stage_event(2, st);
+
+  auto kq = flash_bwd_bf16_kernel<D, false, DROP>;
+  DAD_CUDA(cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                BwdSmem<D>::kBytes));
+  kq<<<grid, kBwdThreads, BwdSmem<D>::kBytes, st>>>(mq, mdo, mk, mv, reinterpret_cast<BF*>(dq),
+                                                   nullptr, lse, delta, S, scale, rate, rng, unit0,
+                                                   status);
+  DAD_LAUNCH_CHECK("flash_bwd_bf16_kernel<dq>");
+  stage_event(3, st);
+  return DADATTN_OK;
+}
+
+}  // namespace
+}  // namespace dadattn
+
+using namespace dadattn;
+
+extern "C" int dadattn_set_stage_events(void** events, int count) {
+  g_stage_events = reinterpret_cast<cudaEvent_t*>(events);
+  g_stage_event_count = events ? count : 0;
+  return DADATTN_OK;
+}
+
+extern "C" size_t dadattn_flash_bwd_bf16_workspace_bytes(int BH, int S, int D) {
+  if (BH <= 0 || S <= 0 || D <= 0) return 0;
+  return static_cast<size_t>(BH) * S * sizeof(float);  // delta [BH,S]
+}
+
+extern "C" int dadattn_flash_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspace,
+                                      size_t workspace_bytes, const uint16_t* dout,
+                                      const uint16_t* out, const float* lse, const uint16_t* q,
+                                      const uint16_t* k, const uint16_t* v, int BH, int S, int D,
+                                      float scale, float rate, uint64_t seed, uint64_t offset,
+                                      int64_t unit0, dadattn_stream_t stream) {
+  if (!dq || !dk || !dv || !workspace || !dout || !out || !lse || !q || !k || !v)
+    return fail(DADATTN_E_ARG, "null tensor pointer");
+  if (BH <= 0 || S <= 0) return fail(DADATTN_E_ARG, "BH=%d and S=%d must be positive", BH, S);
+  if (BH > 65535) return fail(DADATTN_E_UNSUPPORTED, "BH=%d exceeds 65535 per call", BH);
+  if (!dadattn_flash_bf16_supported(D))
+    return fail(DADATTN_E_UNSUPPORTED, "flash attention bf16: unsupported d_head %d", D);
+  if (!(rate >= 0.0f && rate < 1.0f))
+    return fail(DADATTN_E_ARG, "dropout rate %f outside [0,1)", static_cast<double>(rate));
+  for (const void* p : {static_cast<const void*>(dq), static_cast<const void*>(dk),
+                        static_cast<const void*>(dv), static_cast<const void*>(dout),
+                        static_cast<const void*>(out), static_cast<const void*>(q),
+                        static_cast<const void*>(k), static_cast<const void*>(v),
+                        static_cast<const void*>(workspace)})
+    if (!aligned(p, 16)) return fail(DADATTN_E_ARG, "bf16 tensors and workspace must be 16-byte aligned");
+  if (workspace_bytes < dadattn_flash_bwd_bf16_workspace_bytes(BH, S, D))
+    return fail(DADATTN_E_WORKSPACE, "backward workspace %zu < %zu bytes", workspace_bytes,
+                dadattn_flash_bwd_bf16_workspace_bytes(BH, S, D));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* delta = static_cast<float*>(workspace);
+  const bool drop = rate > 0.f;
+#define DAD_BWD16(DH)                                                                            \
+  return drop ? launch_bwd_bf16<DH, true>(dq, dk, dv, delta, dout, out, lse, q, k, v, BH, S,     \
+                                          scale, rate, seed, offset, unit0, st)                  \
+              : launch_bwd_bf16<DH, false>(dq, dk, dv, delta, dout, out, lse, q, k, v, BH, S,    \
+                                           scale, 0.f, 0, 0, 0, st);
+  if (D == 64) {
+    DAD_BWD16(64)
+  }
+  DAD_BWD16(128)
+#undef DAD_BWD16
+}

@@ -5,8 +5,8 @@
  * stream (pass NULL for the legacy default stream, which is what DadGPT itself uses) and
  * returns without synchronising. Return value: 0 on success, a negative DADATTN_E_* code
  * otherwise; dadattn_last_error() then describes the failure (thread-local string).
- * The library allocates nothing unless a function's comment says so; all buffers belong to the
- * caller. There is no CPU fallback: without a CUDA device every compute call fails.
+ * All tensors and workspaces belong to the caller; the library's only allocation is one 4-byte
+ * status word per device (see dadattn_device_status), made on first use and kept until exit. There is no CPU fallback: without a CUDA device every compute call fails.
  *
  * Tensor layouts follow DadGPT: heads already split, [BH, S, D] contiguous, row-major;
  * lse / delta are [BH, S] fp32. "bf16" pointers are raw 16-bit bfloat16 (uint16_t here so the
@@ -97,8 +97,8 @@ int dadattn_flash_fwd_bf16(uint16_t* out, float* lse, const uint16_t* q, const u
 
 /* bf16 form of gpu_flash_attention_backward (reference cuda/attention.cu:241-252). dq,dk,dv bf16,
  * written not accumulated. workspace: caller-owned scratch of at least
- * dadattn_flash_bwd_bf16_workspace_bytes(BH,S,D) bytes, 256-byte aligned (it holds delta and an
- * fp32 dQ accumulator; contents are overwritten). */
+ * dadattn_flash_bwd_bf16_workspace_bytes(BH,S,D) bytes, 16-byte aligned (it takes the place of
+ * the fp32 call's `delta` scratch; contents are overwritten). */
 size_t dadattn_flash_bwd_bf16_workspace_bytes(int BH, int S, int D);
 int dadattn_flash_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspace,
                            size_t workspace_bytes, const uint16_t* dout, const uint16_t* out,
@@ -106,6 +106,12 @@ int dadattn_flash_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* works
                            const uint16_t* v, int BH, int S, int D, float scale, float rate,
                            uint64_t seed, uint64_t offset, int64_t unit0,
                            dadattn_stream_t stream);
+
+/* Measurement aid (no counterpart in the reference): when `events` (an array of `count`
+ * cudaEvent_t) is set for the calling thread, dadattn_flash_bwd_bf16 records events[0] before
+ * its delta kernel, [1] before the dK/dV kernel, [2] before the dQ kernel and [3] after it, on
+ * the call's stream. Pass NULL to switch it off. */
+int dadattn_set_stage_events(void** events, int count);
 
 /* ---- KV-cache decode --------------------------------------------------------------------- */
 

@@ -95,3 +95,88 @@ def test_bf16_matches_fp32_kernel_on_same_inputs(cuda):
     dad.gpu_flash_attention_forward(o32, l32, q.float(), k.float(), v.float(), BH, S, D, 0.125)
     assert (out.float() - o32).abs().max().item() <= 2e-2
     assert (lse - l32).abs().max().item() <= 1e-2
+
+
+def bwd(dout, out, lse, tensors, scale, dev, **kw):
+    tq, tk, tv = tensors
+    BH, S, D = tq.shape
+    tdo, fdo = dev_bf16(dout, dev)
+    dq, dk, dv = (torch.full_like(tq, float("nan")) for _ in range(3))
+    ws = torch.empty(flash_backward_bf16_workspace_bytes(BH, S, D), dtype=torch.uint8, device=dev)
+    dad.gpu_flash_attention_backward_bf16(dq, dk, dv, ws, tdo, out, lse, tq, tk, tv, BH, S, D,
+                                          scale, **kw)
+    assert device_status() == 0
+    return [t.float().cpu().numpy() for t in (dq, dk, dv)], fdo
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("S", [1, 31, 128, 129, 200, 384, 700])
+def test_backward_shapes_against_oracle(cuda, oracle, S, D):
+    rng = np.random.default_rng(31 * D + S)
+    BH = 3
+    q, k, v, dout = (rng.standard_normal((BH, S, D), dtype=np.float32) for _ in range(4))
+    scale = D ** -0.5
+    out, lse, ts, (fq, fk, fv) = fwd(q, k, v, scale, cuda)
+    grads, fdo = bwd(dout, out, lse, ts, scale, cuda)
+    for got, want, name in zip(grads, oracle.backward(fdo, fq, fk, fv, scale), ("dq", "dk", "dv")):
+        assert np.isfinite(got).all(), name
+        assert rel_l2(got, want) <= 3e-2, name
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_backward_dropout_against_oracle(cuda, oracle, D):
+    rng = np.random.default_rng(41)
+    BH, S = 3, 200
+    q, k, v, dout = (rng.standard_normal((BH, S, D), dtype=np.float32) for _ in range(4))
+    scale = D ** -0.5
+    kw = dict(rate=0.1, seed=42, offset=0)
+    out, lse, ts, (fq, fk, fv) = fwd(q, k, v, scale, cuda, **kw)
+    grads, fdo = bwd(dout, out, lse, ts, scale, cuda, **kw)
+    for got, want, name in zip(grads, oracle.backward(fdo, fq, fk, fv, scale, **kw), ("dq", "dk", "dv")):
+        assert rel_l2(got, want) <= 3e-2, name
+    # a shard of the (batch x head) axis reproduces its slice of the whole
+    part, _ = bwd(dout[1:], out[1:].contiguous(), lse[1:].contiguous(), [t[1:].contiguous() for t in ts],
+                  scale, cuda, unit0=1, **kw)
+    for a, b in zip(part, grads):
+        assert np.array_equal(a, b[1:])
+
+
+def test_backward_gpt2_shape_subset_and_properties(cuda, oracle):
+    """Full GPT-2-124M shape with dropout 0.1 (Philox seed 42, offset 0): three (b,h) units against
+    the oracle (each with its own global unit index, which fixes its mask); all units: finite and
+    bit-identical across two calls (no atomics anywhere in the backward)."""
+    shape = W.gpt2(1024)
+    q, k, v = W.qkv(shape)
+    dout = W.dout(shape)
+    kw = dict(rate=0.1, seed=42, offset=0)
+    out, lse, ts, (fq, fk, fv) = fwd(q, k, v, shape.scale, cuda, **kw)
+    grads, fdo = bwd(dout, out, lse, ts, shape.scale, cuda, **kw)
+    units = [0, 100, 191]
+    for u in units:
+        w = oracle.backward(fdo[u:u + 1], fq[u:u + 1], fk[u:u + 1], fv[u:u + 1], shape.scale,
+                            rate=0.1, seed=42, unit0=u)
+        for got, ref, name in zip(grads, w, ("dq", "dk", "dv")):
+            assert rel_l2(got[u:u + 1], ref) <= 3e-2, (u, name)
+    for g in grads:
+        assert np.isfinite(g).all()
+    grads2, _ = bwd(dout, out, lse, ts, shape.scale, cuda, **kw)
+    for a, b in zip(grads, grads2):
+        assert np.array_equal(a, b)
+
+
+def test_backward_matches_fp32_kernel_on_same_inputs(cuda):
+    BH, S, D = 4, 300, 64
+    q, k, v, do = (torch.randn(BH, S, D, device=cuda).to(torch.bfloat16) for _ in range(4))
+    out, lse = torch.empty_like(q), torch.empty(BH, S, device=cuda)
+    dad.gpu_flash_attention_forward_bf16(out, lse, q, k, v, BH, S, D, 0.125)
+    dq, dk, dv = (torch.empty_like(q) for _ in range(3))
+    ws = torch.empty(flash_backward_bf16_workspace_bytes(BH, S, D), dtype=torch.uint8, device=cuda)
+    dad.gpu_flash_attention_backward_bf16(dq, dk, dv, ws, do, out, lse, q, k, v, BH, S, D, 0.125)
+    o32, l32 = torch.empty(BH, S, D, device=cuda), torch.empty(BH, S, device=cuda)
+    f = [t.float() for t in (q, k, v, do)]
+    dad.gpu_flash_attention_forward(o32, l32, f[0], f[1], f[2], BH, S, D, 0.125)
+    g32 = [torch.empty_like(o32) for _ in range(3)]
+    dad.gpu_flash_attention_backward(*g32, torch.empty(BH, S, device=cuda), f[3], o32, l32, f[0], f[1],
+                                     f[2], BH, S, D, 0.125)
+    for a, b in zip((dq, dk, dv), g32):
+        assert rel_l2(a.float().cpu().numpy(), b.cpu().numpy()) <= 3e-2
