@@ -241,20 +241,21 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_arrive(&bars->s_free);  // S is in registers: the next QK^T may overwrite it
 
       const int c0 = j * kBN;
-      float mx = -FLT_MAX;
       if (j == n_kv - 1) {  // the diagonal tile is the only one that needs the causal mask
 #pragma unroll
-        for (int c = 0; c < kBN; ++c) {
-          t[c] = (c0 + c <= r) ? t[c] * scale_log2 : -INFINITY;
-          mx = fmaxf(mx, t[c]);
-        }
-      } else {
-#pragma unroll
-        for (int c = 0; c < kBN; ++c) {
-          t[c] *= scale_log2;
-          mx = fmaxf(mx, t[c]);
-        }
+        for (int c = 0; c < kBN; ++c)
+          if (c0 + c > r) t[c] = -INFINITY;
       }
+      // Row max over the raw scores (scale > 0, so it commutes with the scaling). Eight
+      // independent chains: with one softmax warp per scheduler, a single 128-long dependent
+      // chain would cost its full latency.
+      float mx8[8];
+#pragma unroll
+      for (int a = 0; a < 8; ++a) mx8[a] = t[a];
+#pragma unroll
+      for (int c = 8; c < kBN; ++c) mx8[c & 7] = fmaxf(mx8[c & 7], t[c]);
+      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]))) * scale_log2;
 
       bool waited_o = false;
       if (j == 0) {
@@ -279,13 +280,15 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
         m = m_new;
       }
 
-      float sum = 0.f;
+      // p = exp2(s * scale * log2e - m): one FFMA and one MUFU per score
+      float sum8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      const float neg_m = -m;
 #pragma unroll
       for (int c = 0; c < kBN; ++c) {
-        t[c] = ex2(t[c] - m);
-        sum += t[c];
+        t[c] = ex2(fmaf(t[c], scale_log2, neg_m));
+        sum8[c & 7] += t[c];
       }
-      l += sum;
+      l += ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
       if (DROP) {
         const uint64_t idx0 = (static_cast<uint64_t>(unit0 + bh) * S + r) * S + c0;
 #pragma unroll 4
@@ -386,6 +389,7 @@ extern "C" int dadattn_flash_fwd_bf16(uint16_t* out, float* lse, const uint16_t*
     return fail(DADATTN_E_UNSUPPORTED, "flash attention bf16: unsupported d_head %d", D);
   if (!(rate >= 0.0f && rate < 1.0f))
     return fail(DADATTN_E_ARG, "dropout rate %f outside [0,1)", static_cast<double>(rate));
+  if (!(scale > 0.0f)) return fail(DADATTN_E_ARG, "bf16 forward needs scale > 0");
   if (!aligned(out, 16) || !aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) ||
       !aligned(lse, 4))
     return fail(DADATTN_E_ARG, "bf16 tensors must be 16-byte aligned");
