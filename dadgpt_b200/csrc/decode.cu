@@ -320,3 +320,101 @@ extern "C" int dadattn_decode_f32(float* out, const float* q, const float* k_new
   DAD_LAUNCH_CHECK("decode_splitk_kernel<float>");
   return DADATTN_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Decode without any allocation.
+//
+// Some hosts of this library must not allocate device memory once they are running: a serving
+// process that hands every free byte of HBM to its own cache pool at start-up has nothing left
+// for a later cudaMalloc; a latency-critical decode loop cannot afford the device-wide
+// synchronisation an allocation implies; and DadGPT itself sizes all of its buffers once, in
+// model_alloc / kv_cache_alloc, and never allocates inside generate_tokens. For such callers the
+// split-K partials live in the fixed array below instead of a caller-provided workspace, and
+// the bad-length report goes to a fixed word instead of the lazily allocated status word.
+//
+// The array is part of the library image: every GPU that loads libdadattn.so holds these
+// 8 MiB until the process exits, whether or not this entry point is ever called.
+// ---------------------------------------------------------------------------------------------
+namespace dadattn {
+namespace {
+
+constexpr size_t kNoAllocScratchBytes = size_t(8) << 20;
+static __device__ __align__(256) unsigned char g_decode_scratch[kNoAllocScratchBytes];
+static __device__ int g_decode_noalloc_status;
+
+constexpr int kNoAllocMaxDevices = 64;
+float* g_scratch_ptr[kNoAllocMaxDevices] = {};
+int* g_noalloc_status_ptr[kNoAllocMaxDevices] = {};
+
+// In host code the names g_decode_scratch / g_decode_noalloc_status are only handles; the
+// device addresses a kernel can use come from cudaGetSymbolAddress, per device, with that
+// device current. Looked up on the first call on each device and cached.
+int noalloc_setup(float** scratch, int** status) {
+  int dev = 0;
+  DAD_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kNoAllocMaxDevices)
+    return fail(DADATTN_E_UNSUPPORTED, "device ordinal %d not supported", dev);
+  if (!g_scratch_ptr[dev] || !g_noalloc_status_ptr[dev]) {
+    float* s = nullptr;
+    int* w = nullptr;
+    DAD_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&s), g_decode_scratch));
+    DAD_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&w), g_decode_noalloc_status));
+    g_noalloc_status_ptr[dev] = w;
+    g_scratch_ptr[dev] = s;
+  }
+  *scratch = g_scratch_ptr[dev];
+  *status = g_noalloc_status_ptr[dev];
+  return DADATTN_OK;
+}
+
+template <int DH>
+int launch_decode_noalloc(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
+                          const uint16_t* v_new, uint16_t* k_cache, uint16_t* v_cache,
+                          int32_t* lengths, int B, int H, int max_len, float scale,
+                          float* partial, int* status, cudaStream_t st) {
+  using T = __nv_bfloat16;
+  const int splits = (max_len + kChunk - 1) / kChunk;
+  dim3 grid(splits, H, B), cgrid(H, B);
+  decode_splitk_kernel<T, DH><<<grid, kDecodeWarps * 32, 0, st>>>(
+      reinterpret_cast<T*>(out), partial, reinterpret_cast<const T*>(q),
+      reinterpret_cast<const T*>(k_new), reinterpret_cast<const T*>(v_new),
+      reinterpret_cast<T*>(k_cache), reinterpret_cast<T*>(v_cache), lengths, 0, H, max_len, kChunk,
+      scale, 0, status);
+  DAD_LAUNCH_CHECK("decode_splitk_kernel (no-alloc)");
+  decode_combine_kernel<T, DH><<<cgrid, DH, 0, st>>>(reinterpret_cast<T*>(out), partial, lengths,
+                                                     H, max_len, kChunk, splits);
+  DAD_LAUNCH_CHECK("decode_combine_kernel (no-alloc)");
+  return DADATTN_OK;
+}
+
+}  // namespace
+}  // namespace dadattn
+
+extern "C" int dadattn_decode_bf16_noalloc(uint16_t* out, const uint16_t* q,
+                                           const uint16_t* k_new, const uint16_t* v_new,
+                                           uint16_t* k_cache, uint16_t* v_cache, int32_t* lengths,
+                                           int B, int H, int D, int max_len, float scale,
+                                           dadattn_stream_t stream) {
+  if (!out || !q || !k_new || !v_new || !k_cache || !v_cache || !lengths)
+    return fail(DADATTN_E_ARG, "decode: null pointer");
+  if (B <= 0 || H <= 0 || max_len <= 0 || B > 65535 || H > 65535)
+    return fail(DADATTN_E_ARG, "decode: bad sizes B=%d H=%d max_len=%d", B, H, max_len);
+  if (D != 64 && D != 128) return fail(DADATTN_E_UNSUPPORTED, "decode bf16: unsupported D %d", D);
+  if (!aligned(out, 16) || !aligned(q, 16) || !aligned(k_new, 16) || !aligned(v_new, 16) ||
+      !aligned(k_cache, 16) || !aligned(v_cache, 16))
+    return fail(DADATTN_E_ARG, "decode: pointers must be 16-byte aligned");
+  const size_t need = dadattn_decode_workspace_bytes(B, H, D, max_len);
+  if (need > kNoAllocScratchBytes)
+    return fail(DADATTN_E_WORKSPACE,
+                "decode (no-alloc): B=%d H=%d D=%d max_len=%d needs %zu bytes of split-K scratch, "
+                "the built-in array holds %zu; use dadattn_decode_bf16 with your own workspace",
+                B, H, D, max_len, need, static_cast<size_t>(kNoAllocScratchBytes));
+  float* partial = nullptr;
+  int* status = nullptr;
+  if (int rc = noalloc_setup(&partial, &status)) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return D == 64 ? launch_decode_noalloc<64>(out, q, k_new, v_new, k_cache, v_cache, lengths, B, H,
+                                             max_len, scale, partial, status, st)
+                 : launch_decode_noalloc<128>(out, q, k_new, v_new, k_cache, v_cache, lengths, B,
+                                              H, max_len, scale, partial, status, st);
+}

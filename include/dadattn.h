@@ -137,6 +137,28 @@ int dadattn_decode_bf16(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
                         int32_t* lengths, int B, int H, int D, int max_len, float scale,
                         void* workspace, size_t workspace_bytes, dadattn_stream_t stream);
 
+/* dadattn_decode_bf16 for callers that cannot allocate device memory or hand over a workspace
+ * (no counterpart in the reference). Typical cases: a server that gave all remaining HBM to its
+ * own KV-cache pool at start-up, a decode loop that must not hit the device-wide stall of an
+ * allocation, or DadGPT's own generation loop, which sizes every buffer once in kv_cache_alloc
+ * and never allocates afterwards. Same arguments and results as dadattn_decode_bf16 minus the
+ * workspace: the split-K partials go to a fixed 8 MiB array inside the library image (held by
+ * every GPU that loads the library, until exit). The call performs no cudaMalloc/cudaFree and
+ * uses no allocating routine.
+ *  - Limit: dadattn_decode_workspace_bytes(B,H,D,max_len) must be <= 8 MiB (8388608 bytes),
+ *    e.g. B*H <= 3177 at max_len 1280, D 64; larger shapes return DADATTN_E_WORKSPACE.
+ *  - The first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress); make that first call before starting any stream capture.
+ *  - All calls share the one array and it keeps the previous call's partials. Nothing in it has
+ *    to start at zero (every record is written before it is read within a call), but two calls
+ *    that overlap on the GPU (different streams, or threads) race on it: serialise them.
+ *  - A sequence already at max_len is skipped as in dadattn_decode_bf16, but this variant has
+ *    nowhere to report it (dadattn_device_status belongs to the allocating calls). */
+int dadattn_decode_bf16_noalloc(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
+                                const uint16_t* v_new, uint16_t* k_cache, uint16_t* v_cache,
+                                int32_t* lengths, int B, int H, int D, int max_len, float scale,
+                                dadattn_stream_t stream);
+
 /* Synchronises the stream and returns the sticky device-side status word of this device
  * (0, or a DADATTN_E_* code recorded by a kernel: a bounded wait that ran out, a sequence at
  * max_len). Clears the word. */
