@@ -65,3 +65,4 @@ extern "C" int dadattn_device_status(dadattn_stream_t stream) {
   else if (host != 0) fail(host, "device status %d", host);
   return host;
 }
+

@@ -25,6 +25,10 @@
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
+#ifndef DADATTN_EXP
+#define DADATTN_EXP 0
+#endif
+
 namespace dadattn {
 
 // ---------------------------------------------------------------------------------------------
@@ -91,8 +95,8 @@ struct FwdSmem {
 };
 
 struct FwdBars {
-  uint64_t q_full, k_full[kStages], v_full[kStages], kv_empty[kStages];
-  uint64_t s_full, s_free, p_full, o_done;
+  uint64_t q_full, k_full[kStages], v_full[kStages], k_empty[kStages], v_empty[kStages];
+  uint64_t s_full[2], s_free[2], p_full, o_done;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -106,8 +110,12 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
                       int64_t unit0, int* __restrict__ status) {
   using L = FwdSmem<D>;
   constexpr int kPanels = L::kPanels;
-  constexpr uint32_t kTmemCols = 256;  // S: [0,128)  O: [128, 128 + D)
-  constexpr uint32_t kColS = 0, kColO = 128;
+  // TMEM columns. D = 64: S [0,128), O [128,192) in a 256-column allocation, two CTAs per SM.
+  // D = 128 (one CTA per SM): two S buffers [0,256) so that Q K^T of the next tile runs while
+  // this tile's softmax still reads its scores, O [256,384), 512 columns allocated.
+  constexpr int kSBufs = D == 128 ? 2 : 1;
+  constexpr uint32_t kTmemCols = D == 128 ? 512 : 256;
+  constexpr uint32_t kColS = 0, kColO = 128 * kSBufs;
 
   extern __shared__ __align__(1024) uint8_t smem[];
   FwdBars* bars = reinterpret_cast<FwdBars*>(smem + L::kBars);
@@ -129,10 +137,13 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&bars->k_full[s], 1);
       mbar_init(&bars->v_full[s], 1);
-      mbar_init(&bars->kv_empty[s], 1);
+      mbar_init(&bars->k_empty[s], 1);
+      mbar_init(&bars->v_empty[s], 1);
     }
-    mbar_init(&bars->s_full, 1);
-    mbar_init(&bars->s_free, 128);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->s_full[b], 1);
+      mbar_init(&bars->s_free[b], 128);
+    }
     mbar_init(&bars->p_full, 128);
     mbar_init(&bars->o_done, 1);
     bars->abort_flag = 0;
@@ -158,12 +169,14 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
         tma_load_3d(smem + L::kQ + p * kPanelBytes, &map_q, &bars->q_full, p * 64, q0, bh);
       for (int j = 0; j < n_kv; ++j) {
         const int s = j % kStages, use = j / kStages;
-        if (use > 0 && !mbar_wait(&bars->kv_empty[s], (use - 1) & 1, abort_flag)) break;
         uint8_t* kdst = smem + L::kK + s * kPanels * kPanelBytes;
         uint8_t* vdst = smem + L::kV + s * kPanels * kPanelBytes;
+        // K's slot frees when Q K^T of its previous tenant is done, V's when P V is done
+        if (use > 0 && !mbar_wait(&bars->k_empty[s], (use - 1) & 1, abort_flag)) break;
         mbar_arrive_expect_tx(&bars->k_full[s], kPanels * kPanelBytes);
         for (int p = 0; p < kPanels; ++p)
           tma_load_3d(kdst + p * kPanelBytes, &map_k, &bars->k_full[s], p * 64, j * kBN, bh);
+        if (use > 0 && !mbar_wait(&bars->v_empty[s], (use - 1) & 1, abort_flag)) break;
         mbar_arrive_expect_tx(&bars->v_full[s], kPanels * kPanelBytes);
         for (int p = 0; p < kPanels; ++p)
           tma_load_3d(vdst + p * kPanelBytes, &map_v, &bars->v_full[s], p * 64, j * kBN, bh);
@@ -177,12 +190,14 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
       const uint32_t q_addr = smem_u32(smem + L::kQ);
       const uint32_t p_addr = smem_u32(smem + L::kP);
       bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
+      DAD_TRACE_DECL;
 
       // O[:, 64 pn .. 64 pn + 63] (+)= P_i V_i for tile i
       auto issue_pv = [&](int i) -> bool {
         const int s = i % kStages;
         if (!mbar_wait(&bars->v_full[s], (i / kStages) & 1, abort_flag)) return false;
         if (!mbar_wait(&bars->p_full, i & 1, abort_flag)) return false;
+        DAD_TRACE(1);
         tc_fence_after_sync();
         const uint32_t v_addr = smem_u32(smem + L::kV + s * kPanels * kPanelBytes);
 #pragma unroll
@@ -194,25 +209,30 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
             mma_ss(tmem + kColO + pn * 64, a, b, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
           }
         }
-        mma_commit(&bars->kv_empty[s]);
+        mma_commit(&bars->v_empty[s]);
         mma_commit(&bars->o_done);
+        DAD_TRACE(1);
         return true;
       };
 
       for (int j = 0; ok && j < n_kv; ++j) {
         const int s = j % kStages;
         ok = mbar_wait(&bars->k_full[s], (j / kStages) & 1, abort_flag);
-        if (ok && j > 0) ok = mbar_wait(&bars->s_free, (j - 1) & 1, abort_flag);
+        const int sb = j % kSBufs;
+        if (ok && j >= kSBufs) ok = mbar_wait(&bars->s_free[sb], (j / kSBufs - 1) & 1, abort_flag);
         if (!ok) break;
+        DAD_TRACE(1);
         tc_fence_after_sync();
         const uint32_t k_addr = smem_u32(smem + L::kK + s * kPanels * kPanelBytes);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * kPanelBytes + (kk % 4) * 32;
-          mma_ss(tmem + kColS, make_smem_desc_sw128(q_addr + off, 0),
+          mma_ss(tmem + kColS + sb * 128, make_smem_desc_sw128(q_addr + off, 0),
                  make_smem_desc_sw128(k_addr + off, 0), idesc_s, kk > 0 ? 1u : 0u);
         }
-        mma_commit(&bars->s_full);
+        mma_commit(&bars->k_empty[s]);
+        mma_commit(&bars->s_full[sb]);
+        DAD_TRACE(1);
         if (j > 0) ok = issue_pv(j - 1);
       }
       if (ok) issue_pv(n_kv - 1);
@@ -228,34 +248,38 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
     uint8_t* p_row = smem + L::kP + row * 128;
     float m = -FLT_MAX, l = 0.f;
     bool ok = true;
+    DAD_TRACE_DECL;
 
     for (int j = 0; j < n_kv; ++j) {
-      if (!(ok = mbar_wait(&bars->s_full, j & 1, abort_flag))) break;
+      const int sb = j % kSBufs;
+      const uint32_t tS = tlane + kColS + sb * 128;
+      if (!(ok = mbar_wait(&bars->s_full[sb], (j / kSBufs) & 1, abort_flag))) break;
+      if (warp == 2) DAD_TRACE(0);
       tc_fence_after_sync();
-      float t[kBN];
-#pragma unroll
-      for (int c = 0; c < kBN / 32; ++c)
-        tmem_ld32(tlane + kColS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&t[c * 32]));
-      tmem_wait_ld();
-      tc_fence_before_sync();
-      mbar_arrive(&bars->s_free);  // S is in registers: the next QK^T may overwrite it
-
       const int c0 = j * kBN;
-      if (j == n_kv - 1) {  // the diagonal tile is the only one that needs the causal mask
+      // Only the diagonal tile needs the causal mask: columns beyond `limit` are dropped.
+      const bool diagonal = (j == n_kv - 1);
+      const int limit = r - c0;
+
+      // ---- pass 1: row max of the raw scores (scale > 0 commutes with max). All four
+      // 32-column TMEM loads are in flight together so their latency is paid once. ----
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      {
+        uint32_t x[kBN];
 #pragma unroll
-        for (int c = 0; c < kBN; ++c)
-          if (c0 + c > r) t[c] = -INFINITY;
+        for (int ch = 0; ch < kBN / 32; ++ch)
+          tmem_ld32(tS + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&x[ch * 32]));
+        tmem_wait_ld();
+        if (diagonal) {
+#pragma unroll
+          for (int i = 0; i < kBN; ++i)
+            if (i > limit) x[i] = 0xff800000u;  // -inf
+        }
+#pragma unroll
+        for (int i = 0; i < kBN; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(x[i]));
       }
-      // Row max over the raw scores (scale > 0, so it commutes with the scaling). Eight
-      // independent chains: with one softmax warp per scheduler, a single 128-long dependent
-      // chain would cost its full latency.
-      float mx8[8];
-#pragma unroll
-      for (int a = 0; a < 8; ++a) mx8[a] = t[a];
-#pragma unroll
-      for (int c = 8; c < kBN; ++c) mx8[c & 7] = fmaxf(mx8[c & 7], t[c]);
-      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]))) * scale_log2;
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+      if (warp == 2) DAD_TRACE(0);
 
       bool waited_o = false;
       if (j == 0) {
@@ -266,7 +290,7 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
         tc_fence_after_sync();
         const float m_new = fmaxf(m, mx);
         const float corr = ex2(m - m_new);
-#pragma unroll
+#pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
           uint32_t o[32];
           tmem_ld32(tlane + kColO + c * 32, o);
@@ -279,38 +303,74 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
         l *= corr;
         m = m_new;
       }
-
-      // p = exp2(s * scale * log2e - m): one FFMA and one MUFU per score
-      float sum8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      const float neg_m = -m;
-#pragma unroll
-      for (int c = 0; c < kBN; ++c) {
-        t[c] = ex2(fmaf(t[c], scale_log2, neg_m));
-        sum8[c & 7] += t[c];
-      }
-      l += ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
-      if (DROP) {
-        const uint64_t idx0 = (static_cast<uint64_t>(unit0 + bh) * S + r) * S + c0;
-#pragma unroll 4
-        for (int c = 0; c < kBN; ++c)
-          t[c] = (t[c] != 0.f && philox_keep(rng, idx0 + c, rate)) ? t[c] * keep_scale : 0.f;
-      }
-
       // P_{j-1} must have been consumed by its MMA before the buffer is overwritten
       if (j > 0 && !waited_o && !(ok = mbar_wait(&bars->o_done, (j - 1) & 1, abort_flag))) break;
+
+      // ---- pass 2: p = exp2(s * scale * log2e - m), one FFMA + one MUFU per score; bf16 P goes
+      // to shared memory in the swizzled K-major layout. ----
+      if (warp == 2) DAD_TRACE(0);
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      const float neg_m = -m;
+      // One 32-column chunk: exponentials, row-sum, optional dropout, bf16 pack, swizzled store.
+      auto process = [&](uint32_t (&x)[32], int ch) {
+        if (diagonal) {
 #pragma unroll
-      for (int ch = 0; ch < kBN / 8; ++ch) {
-        uint4 w;
-        w.x = pack_bf16(t[ch * 8 + 0], t[ch * 8 + 1]);
-        w.y = pack_bf16(t[ch * 8 + 2], t[ch * 8 + 3]);
-        w.z = pack_bf16(t[ch * 8 + 4], t[ch * 8 + 5]);
-        w.w = pack_bf16(t[ch * 8 + 6], t[ch * 8 + 7]);
-        const int panel = ch / 8, cc = ch % 8;
-        *reinterpret_cast<uint4*>(p_row + panel * kPanelBytes + ((cc ^ (row & 7)) << 4)) = w;
+          for (int i = 0; i < 32; ++i)
+            if (ch * 32 + i > limit) x[i] = 0xff800000u;
+        }
+        float pv[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+#if DADATTN_EXP == 1
+          pv[i] = fmaf(__uint_as_float(x[i]), scale_log2, neg_m) * 1e-3f;
+#else
+          pv[i] = ex2(fmaf(__uint_as_float(x[i]), scale_log2, neg_m));
+#endif
+          sum4[i & 3] += pv[i];
+        }
+        if (DROP) {
+          const uint64_t idx0 = (static_cast<uint64_t>(unit0 + bh) * S + r) * S + c0 + ch * 32;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            pv[i] = (pv[i] != 0.f && philox_keep(rng, idx0 + i, rate)) ? pv[i] * keep_scale : 0.f;
+        }
+        uint8_t* dst = p_row + (ch >> 1) * kPanelBytes;
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) {
+          uint4 w;
+          w.x = pack_bf16(pv[v4 * 8 + 0], pv[v4 * 8 + 1]);
+          w.y = pack_bf16(pv[v4 * 8 + 2], pv[v4 * 8 + 3]);
+          w.z = pack_bf16(pv[v4 * 8 + 4], pv[v4 * 8 + 5]);
+          w.w = pack_bf16(pv[v4 * 8 + 6], pv[v4 * 8 + 7]);
+          const int chunk = (ch & 1) * 4 + v4;  // 16-byte chunk within the 128-byte row
+#if DADATTN_EXP == 2
+          if (w.x == 0x12345678u)
+#endif
+          *reinterpret_cast<uint4*>(dst + ((chunk ^ (row & 7)) << 4)) = w;
+        }
+      };
+      // Two register buffers: the TMEM load of the next chunk flies while this one is processed.
+      uint32_t xa[32], xb[32];
+      tmem_ld32(tS, xa);
+#pragma unroll 1
+      for (int h = 0; h < kBN / 64; ++h) {
+        tmem_wait_ld();
+        tmem_ld32(tS + (2 * h + 1) * 32, xb);
+        process(xa, 2 * h);
+        tmem_wait_ld();
+        if (h + 1 < kBN / 64) {
+          tmem_ld32(tS + (2 * h + 2) * 32, xa);
+        } else {  // S is fully read: the next QK^T may overwrite it
+          tc_fence_before_sync();
+          mbar_arrive(&bars->s_free[sb]);
+        }
+        process(xb, 2 * h + 1);
       }
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(&bars->p_full);
+      if (warp == 2) DAD_TRACE(0);
     }
 
     // Epilogue: O / l -> bf16, lse in natural-log units of the scaled scores
@@ -375,6 +435,8 @@ int launch_fwd_bf16(uint16_t* out, float* lse, const uint16_t* q, const uint16_t
 }  // namespace dadattn
 
 using namespace dadattn;
+
+DAD_TRACE_READER(dadattn_trace_read_fwd)
 
 extern "C" int dadattn_flash_bf16_supported(int d_head) { return d_head == 64 || d_head == 128; }
 

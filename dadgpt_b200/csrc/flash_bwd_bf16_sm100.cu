@@ -180,13 +180,14 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
       const uint32_t r1 = smem_u32(smem + L::kR1), r2 = smem_u32(smem + L::kR2);
       const uint32_t p_addr = smem_u32(smem + L::kP), ds_addr = smem_u32(smem + L::kDS);
       bool ok = mbar_wait(&bars->r_full, 0, abort_flag);
-      for (int i = 0; ok && i < n_it; ++i) {
+
+      // X1 = R1 C1^T, X2 = R2 C2^T for step i (the caller has made sure X1/X2 are free)
+      auto issue_x = [&](int i) -> bool {
         const int s = i % kStages;
         const uint32_t par = (i / kStages) & 1;
         const uint32_t c1 = smem_u32(smem + L::kC1 + s * L::kTile);
         const uint32_t c2 = smem_u32(smem + L::kC2 + s * L::kTile);
-        if (!(ok = mbar_wait(&bars->c1_full[s], par, abort_flag))) break;
-        if (i > 0 && !(ok = mbar_wait(&bars->x_free, (i - 1) & 1, abort_flag))) break;
+        if (!mbar_wait(&bars->c1_full[s], par, abort_flag)) return false;
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
@@ -194,7 +195,7 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
           mma_ss(tmem + kColX1, make_smem_desc_sw128(r1 + off, 0),
                  make_smem_desc_sw128(c1 + off, 0), idesc_x, kk > 0 ? 1u : 0u);
         }
-        if (!(ok = mbar_wait(&bars->c2_full[s], par, abort_flag))) break;
+        if (!mbar_wait(&bars->c2_full[s], par, abort_flag)) return false;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * kPanelBytes + (kk % 4) * 32;
@@ -202,8 +203,14 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
                  make_smem_desc_sw128(c2 + off, 0), idesc_x, kk > 0 ? 1u : 0u);
         }
         mma_commit(&bars->x_full);
-
-        if (!(ok = mbar_wait(&bars->w_full, i & 1, abort_flag))) break;
+        return true;
+      };
+      // accumulators += (p | ds tiles of step i) . streamed tiles of step i
+      auto issue_acc = [&](int i) -> bool {
+        const int s = i % kStages;
+        const uint32_t c1 = smem_u32(smem + L::kC1 + s * L::kTile);
+        const uint32_t c2 = smem_u32(smem + L::kC2 + s * L::kTile);
+        if (!mbar_wait(&bars->w_full, i & 1, abort_flag)) return false;
         tc_fence_after_sync();
 #pragma unroll
         for (int pn = 0; pn < kPanels; ++pn) {
@@ -222,6 +229,23 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
         }
         mma_commit(&bars->c_empty[s]);
         mma_commit(&bars->acc_done);
+        return true;
+      };
+
+      if (kStages >= 2) {
+        // With two stages of streamed tiles the score GEMMs of step i+1 are issued as soon as
+        // the compute warps have pulled step i's scores into registers, i.e. before the
+        // accumulating GEMMs of step i: the tensor core works while p and ds are being formed.
+        ok = ok && issue_x(0);
+        for (int i = 0; ok && i < n_it; ++i) {
+          if (i + 1 < n_it) ok = mbar_wait(&bars->x_free, i & 1, abort_flag) && issue_x(i + 1);
+          ok = ok && issue_acc(i);
+        }
+      } else {
+        for (int i = 0; ok && i < n_it; ++i) {
+          if (i > 0) ok = mbar_wait(&bars->x_free, (i - 1) & 1, abort_flag);
+          ok = ok && issue_x(i) && issue_acc(i);
+        }
       }
     }
   } else {
@@ -263,13 +287,9 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
       // the previous step's p / ds tiles must have been consumed before they are overwritten
       if (i > 0 && !(ok = mbar_wait(&bars->acc_done, (i - 1) & 1, abort_flag))) break;
 
-#pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
+      // One 32-column chunk of the score tile: p and ds for every element, bf16, swizzled store.
+      auto process = [&](const uint32_t (&x1)[32], const uint32_t (&x2)[32], int ch) {
         const int cbase = half * 64 + ch * 32;  // column within the tile
-        uint32_t x1[32], x2[32];
-        tmem_ld32(tlane + kColX1 + cbase, x1);
-        tmem_ld32(tlane + kColX2 + cbase, x2);
-        tmem_wait_ld();
         uint32_t pw[16], dw[16];
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
@@ -307,9 +327,21 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
           *reinterpret_cast<uint4*>(ds_row + off) =
               make_uint4(dw[4 * v4], dw[4 * v4 + 1], dw[4 * v4 + 2], dw[4 * v4 + 3]);
         }
+      };
+      // The TMEM loads of the second chunk fly while the first is processed.
+      {
+        uint32_t xa1[32], xa2[32], xb1[32], xb2[32];
+        tmem_ld32(tlane + kColX1 + half * 64, xa1);
+        tmem_ld32(tlane + kColX2 + half * 64, xa2);
+        tmem_wait_ld();
+        tmem_ld32(tlane + kColX1 + half * 64 + 32, xb1);
+        tmem_ld32(tlane + kColX2 + half * 64 + 32, xb2);
+        process(xa1, xa2, 0);
+        tmem_wait_ld();
+        tc_fence_before_sync();
+        mbar_arrive(&bars->x_free);  // X1/X2 are in registers: the next step's MMAs may overwrite
+        process(xb1, xb2, 1);
       }
-      tc_fence_before_sync();
-      mbar_arrive(&bars->x_free);
       fence_proxy_async_smem();
       mbar_arrive(&bars->w_full);
     }
