@@ -6,14 +6,20 @@
 // Forward, one CTA per 128 query rows of one (batch, head):
 //   warp 0      TMA producer: Q once, then K/V tiles of 128 keys through a 2-stage ring
 //   warp 1      MMA issuer (one elected lane) and owner of the TMEM allocation:
-//               S = Q K^T (128x128, fp32 in TMEM), O += P V (128xD, fp32 in TMEM)
-//   warps 2-5   softmax: one thread per query row (= one TMEM lane). Reads its row of S with
-//               tcgen05.ld, keeps the running max / sum, writes P as bf16 into shared memory
-//               in the 128-byte-swizzled layout the MMA reads, rescales O in TMEM only when the
-//               row max grew by more than 2^8 (lazy rescale; the final O / l is exact).
-// S_{j+1} is issued as soon as the softmax warps have pulled S_j into registers, so the tensor
-// core works on the next tile while the exponentials of the current one are computed; at D = 64
-// two CTAs share an SM, which hides the rest.
+//               S = Q K^T (128x128, fp32 in TMEM), O_h += P_h V_h per 64-key half h
+//   warps 2-9   softmax, two threads per query row: warps 2-5 own key columns 0-63 of every
+//               tile, warps 6-9 columns 64-127 (a warp may only touch the TMEM lane quadrant
+//               warp_id % 4). Each half keeps its OWN running max / sum and its OWN output
+//               accumulator in TMEM, so the two threads of a row never synchronise inside the
+//               loop; the halves are merged once, in the epilogue (split-K inside the CTA).
+//               Eight softmax warps give every scheduler two (four with two CTAs per SM) warps
+//               to hide the FFMA -> MUFU -> FADD latencies behind each other.
+//               A thread reads its 64 scores with tcgen05.ld, writes P as bf16 into shared
+//               memory in the 128-byte-swizzled layout the MMA reads, and rescales its O half
+//               in TMEM only when its max grew by more than 2^8 (lazy rescale; exact result).
+// S_{j+1} is issued before P_j V_j, so the tensor core works on the next tile while the
+// exponentials of the current one are computed; at D = 64 two CTAs share an SM, at D = 128 the
+// scores are double-buffered in TMEM instead.
 //
 // Every mbarrier wait is bounded (sm100_ptx.cuh). If one runs out, the CTA raises its abort
 // flag, everybody falls through to the common exit, TMEM is freed, and DADATTN_E_TIMEOUT is
@@ -24,10 +30,6 @@
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
-
-#ifndef DADATTN_EXP
-#define DADATTN_EXP 0
-#endif
 
 namespace dadattn {
 
@@ -78,7 +80,8 @@ constexpr int kBM = 128;          // query rows per CTA
 constexpr int kBN = 128;          // keys per tile
 constexpr int kStages = 2;        // K/V ring depth
 constexpr int kPanelBytes = 128 * 128;  // [128 rows][64 bf16], 128-byte rows, swizzled
-constexpr int kFwdThreads = 192;
+constexpr int kFwdThreads = 320;         // producer warp, MMA warp, 8 softmax warps
+constexpr int kSoftmaxThreads = 256;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units: P stays below 2^8
@@ -96,7 +99,7 @@ struct FwdSmem {
 
 struct FwdBars {
   uint64_t q_full, k_full[kStages], v_full[kStages], k_empty[kStages], v_empty[kStages];
-  uint64_t s_full[2], s_free[2], p_full, o_done;
+  uint64_t s_full[2], s_free[2], p_full, o_done, stat_full;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -110,9 +113,9 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
                       int64_t unit0, int* __restrict__ status) {
   using L = FwdSmem<D>;
   constexpr int kPanels = L::kPanels;
-  // TMEM columns. D = 64: S [0,128), O [128,192) in a 256-column allocation, two CTAs per SM.
+  // TMEM columns. D = 64: S [0,128), O_0 [128,192), O_1 [192,256): 256 columns, two CTAs per SM.
   // D = 128 (one CTA per SM): two S buffers [0,256) so that Q K^T of the next tile runs while
-  // this tile's softmax still reads its scores, O [256,384), 512 columns allocated.
+  // this tile's softmax still reads its scores, O_0 [256,384), O_1 [384,512).
   constexpr int kSBufs = D == 128 ? 2 : 1;
   constexpr uint32_t kTmemCols = D == 128 ? 512 : 256;
   constexpr uint32_t kColS = 0, kColO = 128 * kSBufs;
@@ -142,10 +145,11 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars->s_full[b], 1);
-      mbar_init(&bars->s_free[b], 128);
+      mbar_init(&bars->s_free[b], kSoftmaxThreads);
     }
-    mbar_init(&bars->p_full, 128);
+    mbar_init(&bars->p_full, kSoftmaxThreads);
     mbar_init(&bars->o_done, 1);
+    mbar_init(&bars->stat_full, kSoftmaxThreads);
     bars->abort_flag = 0;
     fence_mbar_init();
   }
@@ -187,26 +191,32 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
     if (elect_one()) {
       constexpr uint32_t idesc_s = make_idesc_bf16(kBM, kBN, 0, 0);  // Q, K: K-major
       constexpr uint32_t idesc_o = make_idesc_bf16(kBM, 64, 0, 1);   // P K-major, V MN-major
-      const uint32_t q_addr = smem_u32(smem + L::kQ);
-      const uint32_t p_addr = smem_u32(smem + L::kP);
+      const SmemDescBase q_desc = make_desc_base_sw128(smem_u32(smem + L::kQ), 0);
+      const SmemDescBase p_desc = make_desc_base_sw128(smem_u32(smem + L::kP), 0);
+      const SmemDescBase k_desc0 = make_desc_base_sw128(smem_u32(smem + L::kK), 0);
+      const SmemDescBase v_desc0 = make_desc_base_sw128(smem_u32(smem + L::kV), kPanelBytes);
+      constexpr uint32_t kStageBytes = kPanels * kPanelBytes;
       bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
       DAD_TRACE_DECL;
 
-      // O[:, 64 pn .. 64 pn + 63] (+)= P_i V_i for tile i
+      // O_h[:, 64 pn .. 64 pn + 63] (+)= P_i[:, 64 h .. 64 h + 63] V_i[64 h .. 64 h + 63, :]
       auto issue_pv = [&](int i) -> bool {
         const int s = i % kStages;
         if (!mbar_wait(&bars->v_full[s], (i / kStages) & 1, abort_flag)) return false;
         if (!mbar_wait(&bars->p_full, i & 1, abort_flag)) return false;
         DAD_TRACE(1);
         tc_fence_after_sync();
-        const uint32_t v_addr = smem_u32(smem + L::kV + s * kPanels * kPanelBytes);
+        const SmemDescBase v_desc{v_desc0.lo + s * (kStageBytes >> 4), v_desc0.hi};
 #pragma unroll
-        for (int pn = 0; pn < kPanels; ++pn) {
+        for (int h = 0; h < 2; ++h) {
 #pragma unroll
-          for (int kk = 0; kk < kBN / 16; ++kk) {
-            const uint64_t a = make_smem_desc_sw128(p_addr + (kk / 4) * kPanelBytes + (kk % 4) * 32, 0);
-            const uint64_t b = make_smem_desc_sw128(v_addr + pn * kPanelBytes + kk * 2048, kPanelBytes);
-            mma_ss(tmem + kColO + pn * 64, a, b, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+          for (int pn = 0; pn < kPanels; ++pn) {
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              mma_ss(tmem + kColO + h * D + pn * 64, desc_at(p_desc, h * kPanelBytes + kk * 32),
+                     desc_at(v_desc, pn * kPanelBytes + (h * 4 + kk) * 2048), idesc_o,
+                     (i > 0 || kk > 0) ? 1u : 0u);
+            }
           }
         }
         mma_commit(&bars->v_empty[s]);
@@ -223,12 +233,12 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
         if (!ok) break;
         DAD_TRACE(1);
         tc_fence_after_sync();
-        const uint32_t k_addr = smem_u32(smem + L::kK + s * kPanels * kPanelBytes);
+        const SmemDescBase k_desc{k_desc0.lo + s * (kStageBytes >> 4), k_desc0.hi};
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * kPanelBytes + (kk % 4) * 32;
-          mma_ss(tmem + kColS + sb * 128, make_smem_desc_sw128(q_addr + off, 0),
-                 make_smem_desc_sw128(k_addr + off, 0), idesc_s, kk > 0 ? 1u : 0u);
+          mma_ss(tmem + kColS + sb * 128, desc_at(q_desc, off), desc_at(k_desc, off), idesc_s,
+                 kk > 0 ? 1u : 0u);
         }
         mma_commit(&bars->k_empty[s]);
         mma_commit(&bars->s_full[sb]);
@@ -240,43 +250,44 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
   } else {
     // ------------------------------ softmax ------------------------------
     const int quad = warp % 4;            // TMEM lane quadrant this warp may touch
+    const int half = (warp - 2) / 4;      // which 64 key columns of every tile
     const int row = quad * 32 + lane;     // row within the tile = TMEM lane
     const int r = q0 + row;               // query index
     const uint32_t tlane = tmem + (static_cast<uint32_t>(quad * 32) << 16);
+    const uint32_t tO = tlane + kColO + half * D;  // this half's output accumulator
     const float scale_log2 = scale * kLog2e;
     const float keep_scale = DROP ? 1.0f / (1.0f - rate) : 1.0f;
-    uint8_t* p_row = smem + L::kP + row * 128;
-    float m = -FLT_MAX, l = 0.f;
+    uint8_t* p_row = smem + L::kP + half * kPanelBytes + row * 128;
+    float m = -INFINITY, l = 0.f;  // running max (log2 units, scaled) and sum of this half-row
     bool ok = true;
     DAD_TRACE_DECL;
 
     for (int j = 0; j < n_kv; ++j) {
       const int sb = j % kSBufs;
-      const uint32_t tS = tlane + kColS + sb * 128;
+      const uint32_t tS = tlane + kColS + sb * 128 + half * 64;
       if (!(ok = mbar_wait(&bars->s_full[sb], (j / kSBufs) & 1, abort_flag))) break;
       if (warp == 2) DAD_TRACE(0);
       tc_fence_after_sync();
-      const int c0 = j * kBN;
+      const int c0 = j * kBN + half * 64;  // first key of this thread's 64 columns
       // Only the diagonal tile needs the causal mask: columns beyond `limit` are dropped.
       const bool diagonal = (j == n_kv - 1);
       const int limit = r - c0;
 
-      // ---- pass 1: row max of the raw scores (scale > 0 commutes with max). All four
-      // 32-column TMEM loads are in flight together so their latency is paid once. ----
+      // ---- pass 1: max of the raw scores (scale > 0 commutes with max); both 32-column TMEM
+      // loads are in flight together. ----
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       {
-        uint32_t x[kBN];
-#pragma unroll
-        for (int ch = 0; ch < kBN / 32; ++ch)
-          tmem_ld32(tS + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&x[ch * 32]));
+        uint32_t x[64];
+        tmem_ld32(tS, *reinterpret_cast<uint32_t(*)[32]>(&x[0]));
+        tmem_ld32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&x[32]));
         tmem_wait_ld();
         if (diagonal) {
 #pragma unroll
-          for (int i = 0; i < kBN; ++i)
+          for (int i = 0; i < 64; ++i)
             if (i > limit) x[i] = 0xff800000u;  // -inf
         }
 #pragma unroll
-        for (int i = 0; i < kBN; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(x[i]));
+        for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(x[i]));
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
       if (warp == 2) DAD_TRACE(0);
@@ -289,15 +300,16 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
         waited_o = true;
         tc_fence_after_sync();
         const float m_new = fmaxf(m, mx);
-        const float corr = ex2(m - m_new);
+        // m = -inf: nothing but zeros has been accumulated so far (every earlier column masked)
+        const float corr = (m == -INFINITY) ? 0.f : ex2(m - m_new);
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
           uint32_t o[32];
-          tmem_ld32(tlane + kColO + c * 32, o);
+          tmem_ld32(tO + c * 32, o);
           tmem_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-          tmem_st32(tlane + kColO + c * 32, o);
+          tmem_st32(tO + c * 32, o);
         }
         tmem_wait_st();
         l *= corr;
@@ -305,13 +317,13 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
       }
       // P_{j-1} must have been consumed by its MMA before the buffer is overwritten
       if (j > 0 && !waited_o && !(ok = mbar_wait(&bars->o_done, (j - 1) & 1, abort_flag))) break;
+      if (warp == 2) DAD_TRACE(0);
 
       // ---- pass 2: p = exp2(s * scale * log2e - m), one FFMA + one MUFU per score; bf16 P goes
-      // to shared memory in the swizzled K-major layout. ----
-      if (warp == 2) DAD_TRACE(0);
+      // to shared memory in the swizzled K-major layout. A half-row with no visible key yet has
+      // m = -inf: its scores are all -inf and must give p = 0, not exp2(nan). ----
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      const float neg_m = -m;
-      // One 32-column chunk: exponentials, row-sum, optional dropout, bf16 pack, swizzled store.
+      const float neg_m = (m == -INFINITY) ? 0.f : -m;
       auto process = [&](uint32_t (&x)[32], int ch) {
         if (diagonal) {
 #pragma unroll
@@ -321,11 +333,7 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
         float pv[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-#if DADATTN_EXP == 1
-          pv[i] = fmaf(__uint_as_float(x[i]), scale_log2, neg_m) * 1e-3f;
-#else
           pv[i] = ex2(fmaf(__uint_as_float(x[i]), scale_log2, neg_m));
-#endif
           sum4[i & 3] += pv[i];
         }
         if (DROP) {
@@ -334,7 +342,6 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
           for (int i = 0; i < 32; ++i)
             pv[i] = (pv[i] != 0.f && philox_keep(rng, idx0 + i, rate)) ? pv[i] * keep_scale : 0.f;
         }
-        uint8_t* dst = p_row + (ch >> 1) * kPanelBytes;
 #pragma unroll
         for (int v4 = 0; v4 < 4; ++v4) {
           uint4 w;
@@ -342,29 +349,19 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
           w.y = pack_bf16(pv[v4 * 8 + 2], pv[v4 * 8 + 3]);
           w.z = pack_bf16(pv[v4 * 8 + 4], pv[v4 * 8 + 5]);
           w.w = pack_bf16(pv[v4 * 8 + 6], pv[v4 * 8 + 7]);
-          const int chunk = (ch & 1) * 4 + v4;  // 16-byte chunk within the 128-byte row
-#if DADATTN_EXP == 2
-          if (w.x == 0x12345678u)
-#endif
-          *reinterpret_cast<uint4*>(dst + ((chunk ^ (row & 7)) << 4)) = w;
+          const int chunk = ch * 4 + v4;  // 16-byte chunk within the 128-byte row
+          *reinterpret_cast<uint4*>(p_row + ((chunk ^ (row & 7)) << 4)) = w;
         }
       };
-      // Two register buffers: the TMEM load of the next chunk flies while this one is processed.
-      uint32_t xa[32], xb[32];
-      tmem_ld32(tS, xa);
-#pragma unroll 1
-      for (int h = 0; h < kBN / 64; ++h) {
+      {
+        uint32_t xa[32], xb[32];
+        tmem_ld32(tS, xa);
+        tmem_ld32(tS + 32, xb);
         tmem_wait_ld();
-        tmem_ld32(tS + (2 * h + 1) * 32, xb);
-        process(xa, 2 * h);
-        tmem_wait_ld();
-        if (h + 1 < kBN / 64) {
-          tmem_ld32(tS + (2 * h + 2) * 32, xa);
-        } else {  // S is fully read: the next QK^T may overwrite it
-          tc_fence_before_sync();
-          mbar_arrive(&bars->s_free[sb]);
-        }
-        process(xb, 2 * h + 1);
+        tc_fence_before_sync();
+        mbar_arrive(&bars->s_free[sb]);  // S is in registers: the next QK^T may overwrite it
+        process(xa, 0);
+        process(xb, 1);
       }
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       fence_proxy_async_smem();
@@ -373,29 +370,48 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
       if (warp == 2) DAD_TRACE(0);
     }
 
-    // Epilogue: O / l -> bf16, lse in natural-log units of the scaled scores
-    if (ok && (ok = mbar_wait(&bars->o_done, (n_kv - 1) & 1, abort_flag))) {
+    // Epilogue: merge the two halves of each row. out = (O_0 w_0 + O_1 w_1) / (l_0 w_0 + l_1 w_1)
+    // with w_h = exp2(m_h - max(m_0, m_1)); lse in natural-log units of the scaled scores.
+    // Each thread of the pair writes half of the row's D outputs.
+    // The (max, sum) pairs are exchanged through the Q tile's shared memory, which nobody reads
+    // any more: every Q K^T has completed before the last s_full was observed.
+    float2* stat = reinterpret_cast<float2*>(smem + L::kQ);  // [2][128]
+    if (ok) {
+      stat[half * 128 + row] = make_float2(m, l);
+      mbar_arrive(&bars->stat_full);
+      ok = mbar_wait(&bars->stat_full, 0, abort_flag) &&
+           mbar_wait(&bars->o_done, (n_kv - 1) & 1, abort_flag);
+    }
+    if (ok) {
       tc_fence_after_sync();
-      const float inv = 1.0f / l;
-      __nv_bfloat16* dst = out + (static_cast<size_t>(bh) * S + r) * D;
+      const float2 s0 = stat[row], s1 = stat[128 + row];
+      const float m_tot = fmaxf(s0.x, s1.x);  // half 0 always sees key 0: finite
+      const float w0 = ex2(s0.x - m_tot);
+      const float w1 = (s1.x == -INFINITY) ? 0.f : ex2(s1.x - m_tot);
+      const float l_tot = s0.y * w0 + s1.y * w1;
+      const float f0 = w0 / l_tot, f1 = w1 / l_tot;
+      constexpr int kCols = D / 2;  // output columns per thread
+      __nv_bfloat16* dst = out + (static_cast<size_t>(bh) * S + r) * D + half * kCols;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t o[32];
-        tmem_ld32(tlane + kColO + c * 32, o);
+      for (int c = 0; c < kCols / 32; ++c) {
+        uint32_t oa[32], ob[32];
+        tmem_ld32(tlane + kColO + half * kCols + c * 32, oa);
+        tmem_ld32(tlane + kColO + D + half * kCols + c * 32, ob);
         tmem_wait_ld();
         if (r < S) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            uint4 w;
-            w.x = pack_bf16(__uint_as_float(o[8 * i + 0]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
-            w.y = pack_bf16(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
-            w.z = pack_bf16(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
-            w.w = pack_bf16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c * 32 + i * 8) = w;
+            float y[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              y[e] = __uint_as_float(oa[8 * i + e]) * f0 + __uint_as_float(ob[8 * i + e]) * f1;
+            *reinterpret_cast<uint4*>(dst + c * 32 + i * 8) =
+                make_uint4(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]), pack_bf16(y[4], y[5]),
+                           pack_bf16(y[6], y[7]));
           }
         }
       }
-      if (r < S) lse[static_cast<size_t>(bh) * S + r] = (m + log2f(l)) * kLn2;
+      if (half == 0 && r < S) lse[static_cast<size_t>(bh) * S + r] = (m_tot + log2f(l_tot)) * kLn2;
     }
   }
 

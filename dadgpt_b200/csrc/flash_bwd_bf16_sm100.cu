@@ -5,11 +5,11 @@
 // Nothing is accumulated across CTAs, so there are no atomics and results are deterministic,
 // as in the reference. Both tensor-core kernels are one template:
 //
-//   resident tiles R1,R2 (128 rows)   streamed tiles C1,C2 (128 rows each step)
+//   resident tiles R1,R2 (128 rows)   streamed tiles C1,C2 (64 rows per step)
 //   dK/dV kernel:  K, V               Q, dO      rows of the score tile = keys
 //   dQ    kernel:  Q, dO              K, V       rows of the score tile = queries
 //
-//   X1 = R1 C1^T  (S or S^T)          X2 = R2 C2^T  (dP or dP^T)        -> TMEM, fp32
+//   X1 = R1 C1^T  (S or S^T)          X2 = R2 C2^T  (dP or dP^T)    128 x 64 each, fp32 in TMEM
 //   p  = exp2(X1 * scale * log2e - lse[query] * log2e)
 //   ds = p * (X2 * dropmask/(1-rate) - delta[query]) * scale
 //   dK/dV kernel:  dV += (p*dropmask/(1-rate))^T-tile . C2,  dK += ds-tile . C1
@@ -19,7 +19,12 @@
 // swizzled K-major layout and consumed as the A operand; the streamed tiles serve as the
 // MN-major B operand of the accumulating MMAs, straight from where TMA put them.
 //   warp 0      TMA producer          warp 1      MMA issuer + TMEM owner
-//   warps 2-9   compute: two warps per TMEM lane quadrant, each taking 64 of the 128 columns
+//   warps 2-9   compute: two warps per TMEM lane quadrant, each taking 32 of the 64 columns
+//
+// Streaming 64 rows at a time keeps a CTA at 256 TMEM columns and ~100 KB of shared memory at
+// D = 64, so two CTAs share an SM and one CTA's MMAs run under the other's exponentials. At
+// D = 128 (one CTA per SM) the score tiles are double-buffered in TMEM instead and the streamed
+// tiles get a third stage, so the score GEMMs of step i+2 are issued while step i is computed.
 #include <cuda_bf16.h>
 
 #include <cfloat>
@@ -32,31 +37,37 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kTileRows = 128;
-constexpr int kPanelBytes = 128 * 128;
+constexpr int kTileRows = 128;            // rows owned by a CTA (keys or queries)
+constexpr int kSubRows = 64;              // rows of a streamed tile
+constexpr int kPanelBytes = 128 * 128;    // [128 rows][64 bf16] swizzled panel
+constexpr int kSubPanelBytes = 64 * 128;  // [64 rows][64 bf16] swizzled panel
 constexpr int kBwdThreads = 320;
 constexpr int kComputeThreads = 256;
 constexpr float kLog2e = 1.4426950408889634f;
 
-template <int D>
+template <int D, bool KV>
 struct BwdSmem {
   static constexpr int kPanels = D / 64;
-  static constexpr int kStages = D == 64 ? 2 : 1;
-  static constexpr int kTile = kPanels * kPanelBytes;     // one [128, D] bf16 tile
+  static constexpr int kXBufs = D == 64 ? 1 : 2;           // score-tile buffers in TMEM
+  static constexpr int kStages = 3;                        // streamed-tile ring depth
+  static constexpr int kTile = kPanels * kPanelBytes;      // resident [128, D] tile
+  static constexpr int kSub = kPanels * kSubPanelBytes;    // streamed [64, D] tile
   static constexpr int kR1 = 0;
   static constexpr int kR2 = kR1 + kTile;
   static constexpr int kC1 = kR2 + kTile;
-  static constexpr int kC2 = kC1 + kStages * kTile;
-  static constexpr int kP = kC2 + kStages * kTile;        // [128][128] bf16, two panels
-  static constexpr int kDS = kP + 2 * kPanelBytes;
-  static constexpr int kVec = kDS + 2 * kPanelBytes;      // lse*log2e and delta: [2][2][128] fp32
-  static constexpr int kBars = kVec + 2 * 2 * 128 * 4;
-  static constexpr int kBytes = kBars + 256;
+  static constexpr int kC2 = kC1 + kStages * kSub;
+  static constexpr int kDS = kC2 + kStages * kSub;         // [128][64] bf16, one panel
+  static constexpr int kP = kDS + kPanelBytes;             // only the dK/dV kernel has a p tile
+  static constexpr int kVec = kP + (KV ? kPanelBytes : 0); // lse*log2e, delta: [2][64] fp32
+  static constexpr int kBars = kVec + 2 * 64 * 4;
+  // At D = 64 two CTAs must fit one SM: 2 x (kBytes + 1 KB reserved) <= 228 KB.
+  static constexpr int kBytes = kBars + 192;
+  static_assert(D != 64 || 2 * (kBytes + 1024) <= 233472, "two CTAs per SM no longer fit");
 };
 
 struct BwdBars {
-  uint64_t r_full, c1_full[2], c2_full[2], c_empty[2];
-  uint64_t x_full, x_free, w_full, acc_done, vec_full;
+  uint64_t r_full, c1_full[3], c2_full[3], c_empty[3];
+  uint64_t x_full[2], x_free[2], w_full, acc_done, vec_full;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -88,7 +99,7 @@ __global__ void flash_delta_bf16_kernel(float* __restrict__ delta,
 
 // KV = true: dK/dV kernel (grid.x = key tile). KV = false: dQ kernel (grid.x = query tile).
 template <int D, bool KV, bool DROP>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, D == 64 ? 2 : 1)
 flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
                       const __grid_constant__ CUtensorMap map_r2,
                       const __grid_constant__ CUtensorMap map_c1,
@@ -97,11 +108,13 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
                       const float* __restrict__ lse, const float* __restrict__ delta, int S,
                       float scale, float rate, PhiloxKey rng, int64_t unit0,
                       int* __restrict__ status) {
-  using L = BwdSmem<D>;
+  using L = BwdSmem<D, KV>;
   constexpr int kPanels = L::kPanels;
   constexpr int kStages = L::kStages;
-  constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kColX1 = 0, kColX2 = 128, kColA1 = 256, kColA2 = 256 + D;
+  constexpr int kXBufs = L::kXBufs;
+  // TMEM: per score buffer X1 [0,64) X2 [64,128); accumulators after the score buffers.
+  constexpr uint32_t kTmemCols = D == 64 ? 256 : 512;
+  constexpr uint32_t kColA1 = 128 * kXBufs, kColA2 = kColA1 + D;
 
   extern __shared__ __align__(1024) uint8_t smem[];
   BwdBars* bars = reinterpret_cast<BwdBars*>(smem + L::kBars);
@@ -110,12 +123,13 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int n_tiles = (S + kTileRows - 1) / kTileRows;
+  const int n_sub = (S + kSubRows - 1) / kSubRows;
   const int bh = blockIdx.y;
-  // dK/dV: key tile kt streams query tiles kt..n-1 (low kt = most work = scheduled first).
-  // dQ:    query tile qt streams key tiles 0..qt   (high qt first).
+  // dK/dV: key tile `own` streams the query sub-tiles 2*own .. n_sub-1 (low `own` = most work =
+  // scheduled first). dQ: query tile `own` streams the key sub-tiles 0 .. min(2*own+1, n_sub-1).
   const int own = KV ? static_cast<int>(blockIdx.x) : n_tiles - 1 - static_cast<int>(blockIdx.x);
-  const int first = KV ? own : 0;
-  const int n_it = KV ? n_tiles - own : own + 1;
+  const int first = KV ? 2 * own : 0;
+  const int n_it = KV ? n_sub - 2 * own : min(2 * own + 2, n_sub);
   const int row0 = own * kTileRows;
 
   if ((smem_u32(smem) & 1023u) != 0) {
@@ -124,13 +138,15 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
   }
   if (threadIdx.x == 0) {
     mbar_init(&bars->r_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < 3; ++s) {
       mbar_init(&bars->c1_full[s], 1);
       mbar_init(&bars->c2_full[s], 1);
       mbar_init(&bars->c_empty[s], 1);
     }
-    mbar_init(&bars->x_full, 1);
-    mbar_init(&bars->x_free, kComputeThreads);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->x_full[b], 1);
+      mbar_init(&bars->x_free[b], kComputeThreads);
+    }
     mbar_init(&bars->w_full, kComputeThreads);
     mbar_init(&bars->acc_done, 1);
     mbar_init(&bars->vec_full, kComputeThreads);
@@ -161,98 +177,102 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
       for (int i = 0; i < n_it; ++i) {
         const int s = i % kStages, use = i / kStages;
         if (use > 0 && !mbar_wait(&bars->c_empty[s], (use - 1) & 1, abort_flag)) break;
-        const int c_row0 = (first + i) * kTileRows;
-        mbar_arrive_expect_tx(&bars->c1_full[s], L::kTile);
+        const int c_row0 = (first + i) * kSubRows;
+        mbar_arrive_expect_tx(&bars->c1_full[s], L::kSub);
         for (int p = 0; p < kPanels; ++p)
-          tma_load_3d(smem + L::kC1 + s * L::kTile + p * kPanelBytes, &map_c1, &bars->c1_full[s],
-                      p * 64, c_row0, bh);
-        mbar_arrive_expect_tx(&bars->c2_full[s], L::kTile);
+          tma_load_3d(smem + L::kC1 + s * L::kSub + p * kSubPanelBytes, &map_c1,
+                      &bars->c1_full[s], p * 64, c_row0, bh);
+        mbar_arrive_expect_tx(&bars->c2_full[s], L::kSub);
         for (int p = 0; p < kPanels; ++p)
-          tma_load_3d(smem + L::kC2 + s * L::kTile + p * kPanelBytes, &map_c2, &bars->c2_full[s],
-                      p * 64, c_row0, bh);
+          tma_load_3d(smem + L::kC2 + s * L::kSub + p * kSubPanelBytes, &map_c2,
+                      &bars->c2_full[s], p * 64, c_row0, bh);
       }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     if (elect_one()) {
-      constexpr uint32_t idesc_x = make_idesc_bf16(128, 128, 0, 0);  // both operands K-major
-      constexpr uint32_t idesc_a = make_idesc_bf16(128, 64, 0, 1);   // B = streamed tile, MN-major
-      const uint32_t r1 = smem_u32(smem + L::kR1), r2 = smem_u32(smem + L::kR2);
-      const uint32_t p_addr = smem_u32(smem + L::kP), ds_addr = smem_u32(smem + L::kDS);
+      constexpr uint32_t idesc_x = make_idesc_bf16(128, 64, 0, 0);  // both operands K-major
+      constexpr uint32_t idesc_a = make_idesc_bf16(128, 64, 0, 1);  // B = streamed tile, MN-major
+      const SmemDescBase r1 = make_desc_base_sw128(smem_u32(smem + L::kR1), 0);
+      const SmemDescBase r2 = make_desc_base_sw128(smem_u32(smem + L::kR2), 0);
+      const SmemDescBase p_desc = make_desc_base_sw128(smem_u32(smem + L::kP), 0);
+      const SmemDescBase ds_desc = make_desc_base_sw128(smem_u32(smem + L::kDS), 0);
+      const SmemDescBase c1_desc0 = make_desc_base_sw128(smem_u32(smem + L::kC1), kSubPanelBytes);
+      const SmemDescBase c2_desc0 = make_desc_base_sw128(smem_u32(smem + L::kC2), kSubPanelBytes);
       bool ok = mbar_wait(&bars->r_full, 0, abort_flag);
+      DAD_TRACE_DECL;
 
-      // X1 = R1 C1^T, X2 = R2 C2^T for step i (the caller has made sure X1/X2 are free)
+      // X1 = R1 C1^T, X2 = R2 C2^T for step i into score buffer i % kXBufs (the caller has made
+      // sure that buffer is free)
       auto issue_x = [&](int i) -> bool {
-        const int s = i % kStages;
+        const int s = i % kStages, xb = i % kXBufs;
         const uint32_t par = (i / kStages) & 1;
-        const uint32_t c1 = smem_u32(smem + L::kC1 + s * L::kTile);
-        const uint32_t c2 = smem_u32(smem + L::kC2 + s * L::kTile);
+        const SmemDescBase c1{c1_desc0.lo + s * (L::kSub >> 4), c1_desc0.hi};
+        const SmemDescBase c2{c2_desc0.lo + s * (L::kSub >> 4), c2_desc0.hi};
         if (!mbar_wait(&bars->c1_full[s], par, abort_flag)) return false;
+        DAD_TRACE(1);
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * kPanelBytes + (kk % 4) * 32;
-          mma_ss(tmem + kColX1, make_smem_desc_sw128(r1 + off, 0),
-                 make_smem_desc_sw128(c1 + off, 0), idesc_x, kk > 0 ? 1u : 0u);
+          mma_ss(tmem + xb * 128, desc_at(r1, (kk / 4) * kPanelBytes + (kk % 4) * 32),
+                 desc_at(c1, (kk / 4) * kSubPanelBytes + (kk % 4) * 32), idesc_x,
+                 kk > 0 ? 1u : 0u);
         }
         if (!mbar_wait(&bars->c2_full[s], par, abort_flag)) return false;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * kPanelBytes + (kk % 4) * 32;
-          mma_ss(tmem + kColX2, make_smem_desc_sw128(r2 + off, 0),
-                 make_smem_desc_sw128(c2 + off, 0), idesc_x, kk > 0 ? 1u : 0u);
+          mma_ss(tmem + xb * 128 + 64, desc_at(r2, (kk / 4) * kPanelBytes + (kk % 4) * 32),
+                 desc_at(c2, (kk / 4) * kSubPanelBytes + (kk % 4) * 32), idesc_x,
+                 kk > 0 ? 1u : 0u);
         }
-        mma_commit(&bars->x_full);
+        mma_commit(&bars->x_full[xb]);
+        DAD_TRACE(1);
         return true;
       };
-      // accumulators += (p | ds tiles of step i) . streamed tiles of step i
+      // accumulators += (p | ds tiles of step i) . streamed tiles of step i (K = 64 rows)
       auto issue_acc = [&](int i) -> bool {
         const int s = i % kStages;
-        const uint32_t c1 = smem_u32(smem + L::kC1 + s * L::kTile);
-        const uint32_t c2 = smem_u32(smem + L::kC2 + s * L::kTile);
+        const SmemDescBase c1{c1_desc0.lo + s * (L::kSub >> 4), c1_desc0.hi};
+        const SmemDescBase c2{c2_desc0.lo + s * (L::kSub >> 4), c2_desc0.hi};
         if (!mbar_wait(&bars->w_full, i & 1, abort_flag)) return false;
+        DAD_TRACE(1);
         tc_fence_after_sync();
 #pragma unroll
         for (int pn = 0; pn < kPanels; ++pn) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const uint32_t a_off = (kk / 4) * kPanelBytes + (kk % 4) * 32;
-            const uint32_t b_off = pn * kPanelBytes + kk * 2048;
+          for (int kk = 0; kk < kSubRows / 16; ++kk) {
+            const uint32_t a_off = kk * 32;
+            const uint32_t b_off = pn * kSubPanelBytes + kk * 2048;
             const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
             if (KV) {
-              mma_ss(tmem + kColA1 + pn * 64, make_smem_desc_sw128(p_addr + a_off, 0),
-                     make_smem_desc_sw128(c2 + b_off, kPanelBytes), idesc_a, acc);
+              mma_ss(tmem + kColA1 + pn * 64, desc_at(p_desc, a_off), desc_at(c2, b_off), idesc_a,
+                     acc);
             }
-            mma_ss(tmem + (KV ? kColA2 : kColA1) + pn * 64, make_smem_desc_sw128(ds_addr + a_off, 0),
-                   make_smem_desc_sw128(c1 + b_off, kPanelBytes), idesc_a, acc);
+            mma_ss(tmem + (KV ? kColA2 : kColA1) + pn * 64, desc_at(ds_desc, a_off),
+                   desc_at(c1, b_off), idesc_a, acc);
           }
         }
         mma_commit(&bars->c_empty[s]);
         mma_commit(&bars->acc_done);
+        DAD_TRACE(1);
         return true;
       };
 
-      if (kStages >= 2) {
-        // With two stages of streamed tiles the score GEMMs of step i+1 are issued as soon as
-        // the compute warps have pulled step i's scores into registers, i.e. before the
-        // accumulating GEMMs of step i: the tensor core works while p and ds are being formed.
-        ok = ok && issue_x(0);
-        for (int i = 0; ok && i < n_it; ++i) {
-          if (i + 1 < n_it) ok = mbar_wait(&bars->x_free, i & 1, abort_flag) && issue_x(i + 1);
-          ok = ok && issue_acc(i);
-        }
-      } else {
-        for (int i = 0; ok && i < n_it; ++i) {
-          if (i > 0) ok = mbar_wait(&bars->x_free, (i - 1) & 1, abort_flag);
-          ok = ok && issue_x(i) && issue_acc(i);
-        }
+      // Score GEMMs run kXBufs steps ahead of the accumulating GEMMs: step i + kXBufs is issued
+      // as soon as the compute warps have pulled step i's scores out of its buffer.
+      for (int i = 0; ok && i < kXBufs && i < n_it; ++i) ok = issue_x(i);
+      for (int i = 0; ok && i < n_it; ++i) {
+        if (i + kXBufs < n_it)
+          ok = mbar_wait(&bars->x_free[i % kXBufs], (i / kXBufs) & 1, abort_flag) &&
+               issue_x(i + kXBufs);
+        ok = ok && issue_acc(i);
       }
     }
   } else {
     // ------------------------------ compute warps ------------------------------
     const int cw = warp - 2;              // 0..7
     const int quad = warp % 4;            // TMEM lane quadrant of this warp
-    const int half = cw / 4;              // which 64 columns of the 128
+    const int half = cw / 4;              // which 32 columns of the 64
     const int ct = cw * 32 + lane;        // 0..255 among the compute threads
     const int row = quad * 32 + lane;     // row of the score tile = TMEM lane
     const int grow = row0 + row;          // key (KV) or query (dQ) index of this row
@@ -268,82 +288,98 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
       row_delta = grow < S ? delta[vec_base + grow] : 0.f;
     }
     bool ok = true;
+    DAD_TRACE_DECL;
 
     for (int i = 0; i < n_it; ++i) {
-      const int col0 = (first + i) * kTileRows;  // first query (KV) / key (dQ) of the streamed tile
-      const bool diagonal = KV ? (i == 0) : (i == n_it - 1);
-      float* v_lse = vec + (i & 1) * 256;
-      float* v_delta = v_lse + 128;
-      if (KV) {  // per-column vectors of this query tile
-        const int q = col0 + (ct & 127);
-        if (ct < 128) v_lse[ct] = q < S ? lse[vec_base + q] * kLog2e : INFINITY;
-        else v_delta[ct - 128] = q < S ? delta[vec_base + q] : 0.f;
+      if (warp == 2) DAD_TRACE(0);
+      const int col0 = (first + i) * kSubRows;  // first query (KV) / key (dQ) of the streamed tile
+      // sub-tiles that straddle the diagonal need the causal comparison
+      const bool diagonal = KV ? (i < 2) : (first + i >= 2 * own);
+      const int xb = i % kXBufs;
+      float* v_lse = vec;
+      float* v_delta = vec + 64;
+      if (KV) {  // per-column vectors of this query sub-tile (one buffer)
+        // w_full(i-1) complete = every compute thread is done with step i-1, reads of the
+        // vectors included, so they may be overwritten
+        if (i > 0 && !(ok = mbar_wait(&bars->w_full, (i - 1) & 1, abort_flag))) break;
+        if (ct < 128) {
+          const int q = col0 + (ct & 63);
+          if (ct < 64) v_lse[ct] = q < S ? lse[vec_base + q] * kLog2e : INFINITY;
+          else v_delta[ct - 64] = q < S ? delta[vec_base + q] : 0.f;
+        }
         // an mbarrier rather than a named barrier: its wait is bounded like every other one
         mbar_arrive(&bars->vec_full);
         if (!(ok = mbar_wait(&bars->vec_full, i & 1, abort_flag))) break;
       }
-      if (!(ok = mbar_wait(&bars->x_full, i & 1, abort_flag))) break;
+      if (!(ok = mbar_wait(&bars->x_full[xb], (i / kXBufs) & 1, abort_flag))) break;
+      if (warp == 2) DAD_TRACE(0);
       tc_fence_after_sync();
-      // the previous step's p / ds tiles must have been consumed before they are overwritten
-      if (i > 0 && !(ok = mbar_wait(&bars->acc_done, (i - 1) & 1, abort_flag))) break;
 
-      // One 32-column chunk of the score tile: p and ds for every element, bf16, swizzled store.
-      auto process = [&](const uint32_t (&x1)[32], const uint32_t (&x2)[32], int ch) {
-        const int cbase = half * 64 + ch * 32;  // column within the tile
-        uint32_t pw[16], dw[16];
+      const int cbase = half * 32;  // this thread's columns within the 64
+      uint32_t x1[32], x2[32];
+      tmem_ld32(tlane + xb * 128 + cbase, x1);
+      tmem_ld32(tlane + xb * 128 + 64 + cbase, x2);
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      mbar_arrive(&bars->x_free[xb]);  // scores are in registers: the buffer may be overwritten
+      if (warp == 2) DAD_TRACE(0);
+
+      uint32_t pw[16], dw[16];
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float pv[2], dv[2];
+      for (int c = 0; c < 32; c += 4) {
+        float l2[4], dl[4];
+        if (KV) {  // 128-bit broadcast reads: all lanes of a warp want the same four columns
+          const float4 a = *reinterpret_cast<const float4*>(v_lse + cbase + c);
+          const float4 b = *reinterpret_cast<const float4*>(v_delta + cbase + c);
+          l2[0] = a.x; l2[1] = a.y; l2[2] = a.z; l2[3] = a.w;
+          dl[0] = b.x; dl[1] = b.y; dl[2] = b.z; dl[3] = b.w;
+        } else {
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int col = cbase + c + e;
-            const int gcol = col0 + col;
-            const int key = KV ? grow : gcol, query = KV ? gcol : grow;
-            const float l2 = KV ? v_lse[col] : row_lse2;
-            const float dl = KV ? v_delta[col] : row_delta;
-            float p = ex2(fmaf(__uint_as_float(x1[c + e]), scale_log2, -l2));
-            if (diagonal && key > query) p = 0.f;
-            float g = __uint_as_float(x2[c + e]);
-            float pd = p;
-            if (DROP) {
-              const uint64_t idx = (static_cast<uint64_t>(unit0 + bh) * S + query) * S + key;
-              const float mk = (p != 0.f && philox_keep(rng, idx, rate)) ? keep_scale : 0.f;
-              pd = p * mk;
-              g *= mk;
-            }
-            pv[e] = pd;
-            dv[e] = p * (g - dl) * scale;
+          for (int e = 0; e < 4; ++e) {
+            l2[e] = row_lse2;
+            dl[e] = row_delta;
           }
-          pw[c / 2] = pack_bf16(pv[0], pv[1]);
-          dw[c / 2] = pack_bf16(dv[0], dv[1]);
         }
+        float pv[4], dv[4];
 #pragma unroll
-        for (int v4 = 0; v4 < 4; ++v4) {
-          const int chunk = (ch * 32) / 8 + v4;  // 16-byte chunk within this half's panel
-          const int off = half * kPanelBytes + ((chunk ^ (row & 7)) << 4);
-          if (KV)
-            *reinterpret_cast<uint4*>(p_row + off) =
-                make_uint4(pw[4 * v4], pw[4 * v4 + 1], pw[4 * v4 + 2], pw[4 * v4 + 3]);
-          *reinterpret_cast<uint4*>(ds_row + off) =
-              make_uint4(dw[4 * v4], dw[4 * v4 + 1], dw[4 * v4 + 2], dw[4 * v4 + 3]);
+        for (int e = 0; e < 4; ++e) {
+          const int gcol = col0 + cbase + c + e;
+          const int key = KV ? grow : gcol, query = KV ? gcol : grow;
+          float p = ex2(fmaf(__uint_as_float(x1[c + e]), scale_log2, -l2[e]));
+          if (diagonal && key > query) p = 0.f;
+          float g = __uint_as_float(x2[c + e]);
+          float pd = p;
+          if (DROP) {
+            const uint64_t idx = (static_cast<uint64_t>(unit0 + bh) * S + query) * S + key;
+            const float mk = (p != 0.f && philox_keep(rng, idx, rate)) ? keep_scale : 0.f;
+            pd = p * mk;
+            g *= mk;
+          }
+          pv[e] = pd;
+          dv[e] = p * (g - dl[e]) * scale;
         }
-      };
-      // The TMEM loads of the second chunk fly while the first is processed.
-      {
-        uint32_t xa1[32], xa2[32], xb1[32], xb2[32];
-        tmem_ld32(tlane + kColX1 + half * 64, xa1);
-        tmem_ld32(tlane + kColX2 + half * 64, xa2);
-        tmem_wait_ld();
-        tmem_ld32(tlane + kColX1 + half * 64 + 32, xb1);
-        tmem_ld32(tlane + kColX2 + half * 64 + 32, xb2);
-        process(xa1, xa2, 0);
-        tmem_wait_ld();
-        tc_fence_before_sync();
-        mbar_arrive(&bars->x_free);  // X1/X2 are in registers: the next step's MMAs may overwrite
-        process(xb1, xb2, 1);
+        pw[c / 2] = pack_bf16(pv[0], pv[1]);
+        pw[c / 2 + 1] = pack_bf16(pv[2], pv[3]);
+        dw[c / 2] = pack_bf16(dv[0], dv[1]);
+        dw[c / 2 + 1] = pack_bf16(dv[2], dv[3]);
+      }
+      // the previous step's p / ds tiles must have been consumed before they are overwritten
+      if (warp == 2) DAD_TRACE(0);
+      if (i > 0 && !(ok = mbar_wait(&bars->acc_done, (i - 1) & 1, abort_flag))) break;
+      if (warp == 2) DAD_TRACE(0);
+#pragma unroll
+      for (int v4 = 0; v4 < 4; ++v4) {
+        const int chunk = half * 4 + v4;  // 16-byte chunk within the 128-byte row
+        const int off = (chunk ^ (row & 7)) << 4;
+        if (KV)
+          *reinterpret_cast<uint4*>(p_row + off) =
+              make_uint4(pw[4 * v4], pw[4 * v4 + 1], pw[4 * v4 + 2], pw[4 * v4 + 3]);
+        *reinterpret_cast<uint4*>(ds_row + off) =
+            make_uint4(dw[4 * v4], dw[4 * v4 + 1], dw[4 * v4 + 2], dw[4 * v4 + 3]);
       }
       fence_proxy_async_smem();
       mbar_arrive(&bars->w_full);
+      if (warp == 2) DAD_TRACE(0);
     }
 
     // Epilogue. dK/dV kernel: half 0 stores dV, half 1 stores dK. dQ kernel: halves split D.
@@ -393,11 +429,16 @@ int launch_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, float* delta, cons
                     const uint16_t* out, const float* lse, const uint16_t* q, const uint16_t* k,
                     const uint16_t* v, int BH, int S, float scale, float rate, uint64_t seed,
                     uint64_t offset, int64_t unit0, cudaStream_t st) {
-  CUtensorMap mq, mk, mv, mdo;
+  // resident tiles are loaded with 128-row boxes, streamed tiles with 64-row boxes
+  CUtensorMap mq, mk, mv, mdo, mq_s, mk_s, mv_s, mdo_s;
   if (int rc = make_tensor_map_bf16(&mq, q, BH, S, D, kTileRows)) return rc;
   if (int rc = make_tensor_map_bf16(&mk, k, BH, S, D, kTileRows)) return rc;
   if (int rc = make_tensor_map_bf16(&mv, v, BH, S, D, kTileRows)) return rc;
   if (int rc = make_tensor_map_bf16(&mdo, dout, BH, S, D, kTileRows)) return rc;
+  if (int rc = make_tensor_map_bf16(&mq_s, q, BH, S, D, kSubRows)) return rc;
+  if (int rc = make_tensor_map_bf16(&mk_s, k, BH, S, D, kSubRows)) return rc;
+  if (int rc = make_tensor_map_bf16(&mv_s, v, BH, S, D, kSubRows)) return rc;
+  if (int rc = make_tensor_map_bf16(&mdo_s, dout, BH, S, D, kSubRows)) return rc;
   int* status = device_status_word();
   if (!status) return DADATTN_E_CUDA;
   using BF = __nv_bfloat16;
@@ -414,8 +455,8 @@ int launch_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, float* delta, cons
   dim3 grid((S + kTileRows - 1) / kTileRows, BH);
   auto kkv = flash_bwd_bf16_kernel<D, true, DROP>;
   DAD_CUDA(cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                BwdSmem<D>::kBytes));
-  kkv<<<grid, kBwdThreads, BwdSmem<D>::kBytes, st>>>(mk, mv, mq, mdo, reinterpret_cast<BF*>(dv),
+                                BwdSmem<D, true>::kBytes));
+  kkv<<<grid, kBwdThreads, BwdSmem<D, true>::kBytes, st>>>(mk, mv, mq_s, mdo_s, reinterpret_cast<BF*>(dv),
                                                     reinterpret_cast<BF*>(dk), lse, delta, S,
                                                     scale, rate, rng, unit0, status);
   DAD_LAUNCH_CHECK("flash_bwd_bf16_kernel<dkdv>");
@@ -423,8 +464,8 @@ int launch_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, float* delta, cons
 
   auto kq = flash_bwd_bf16_kernel<D, false, DROP>;
   DAD_CUDA(cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                BwdSmem<D>::kBytes));
-  kq<<<grid, kBwdThreads, BwdSmem<D>::kBytes, st>>>(mq, mdo, mk, mv, reinterpret_cast<BF*>(dq),
+                                BwdSmem<D, false>::kBytes));
+  kq<<<grid, kBwdThreads, BwdSmem<D, false>::kBytes, st>>>(mq, mdo, mk_s, mv_s, reinterpret_cast<BF*>(dq),
                                                    nullptr, lse, delta, S, scale, rate, rng, unit0,
                                                    status);
   DAD_LAUNCH_CHECK("flash_bwd_bf16_kernel<dq>");
@@ -436,6 +477,8 @@ int launch_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, float* delta, cons
 }  // namespace dadattn
 
 using namespace dadattn;
+
+DAD_TRACE_READER(dadattn_trace_read_bwd)
 
 extern "C" int dadattn_set_stage_events(void** events, int count) {
   g_stage_events = reinterpret_cast<cudaEvent_t*>(events);

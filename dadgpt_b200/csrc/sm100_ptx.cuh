@@ -168,6 +168,21 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
   return d;
 }
 
+// The same descriptor split in halves so that the issuing thread spends one 32-bit add per MMA:
+// `hi` is constant for a tile, `lo` carries the start address (in 16-byte units) and the LBO.
+struct SmemDescBase {
+  uint32_t lo, hi;
+};
+__device__ __forceinline__ SmemDescBase make_desc_base_sw128(uint32_t smem_addr, uint32_t lbo_bytes) {
+  const uint64_t d = make_smem_desc_sw128(smem_addr, lbo_bytes);
+  return SmemDescBase{static_cast<uint32_t>(d), static_cast<uint32_t>(d >> 32)};
+}
+// Descriptor of the same tile advanced by `byte_offset` (a multiple of 16 that stays inside the
+// tile, so the 14-bit address field cannot carry into its neighbours).
+__device__ __forceinline__ uint64_t desc_at(SmemDescBase b, uint32_t byte_offset) {
+  return (static_cast<uint64_t>(b.hi) << 32) | static_cast<uint64_t>(b.lo + (byte_offset >> 4));
+}
+
 // ---- tcgen05.ld / st: 32 lanes x 32-bit, N consecutive columns per thread ---------------------
 // A warp may only touch the TMEM lane quadrant (warp_id % 4) * 32 .. + 31.
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
