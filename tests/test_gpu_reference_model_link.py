@@ -1,0 +1,23 @@
+"""GPU: the reference's own model code (src/model.cpp, cuda/gpu_ops.cu, compiled unmodified)
+linked against libdadattn_gpuops.so in place of its cuda/attention.cu (oracle/Makefile target
+_ref/ref_model_link_check). Reproduces, at the model level, the relations the reference's tests
+pin for this path: fused == materialized (tests/test_backward.cpp:432-480) and prefill + cached
+decode == full forward (tests/test_model.cpp:375-414), both at 1e-4."""
+import os
+import subprocess
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+BIN = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref",
+                   "ref_model_link_check")
+
+
+def test_reference_model_runs_on_our_kernels(cuda):
+    if not os.path.exists(BIN):
+        pytest.skip("oracle/_ref/ref_model_link_check not built (reference tree absent at build time)")
+    r = subprocess.run([BIN], capture_output=True, text=True, timeout=300)
+    print(r.stdout, r.stderr)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "ALL OK" in r.stdout
+    assert r.stdout.count(" OK") >= 4
