@@ -129,7 +129,8 @@ class KVCacheBF16:
         self.v = torch.zeros_like(self.k)
         self.lengths = torch.zeros(B, dtype=torch.int32, device=device)
         nbytes = int(_lib.load().dadattn_decode_workspace_bytes(B, H, D, max_len))
-        self.workspace = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        # zero-filled once: the split-K tickets must start at zero (include/dadattn.h)
+        self.workspace = torch.zeros(nbytes, dtype=torch.uint8, device=device)
 
 
 def decode_attention_bf16(out, q, k_new, v_new, cache: KVCacheBF16, scale):

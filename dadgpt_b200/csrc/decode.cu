@@ -1,20 +1,29 @@
 // KV-cache decode attention: one new query token per sequence against that sequence's cache.
 //
 // The reference runs this as 61 tiny launches per layer (per-head M=1 cuBLAS products, 256-byte
-// device-to-device appends, one softmax; src/model.cpp:745-790). Here it is one split-K kernel
-// plus a small combine kernel per layer call, for any number of concurrent sequences:
-//   * grid = (splits, heads, sequences); a CTA owns `chunk` consecutive cache rows of one
-//     (sequence, head) and exits at once when the chunk lies beyond the sequence's length;
+// device-to-device appends, one softmax; src/model.cpp:745-790). Here it is ONE split-K kernel
+// per layer call, for any number of concurrent sequences:
+//   * grid = (sequences x heads, splits); a CTA of 8 warps owns `chunk` consecutive cache rows
+//     of one (sequence, head): the whole sequence when there are enough pairs to fill the GPU,
+//     a slice otherwise. Splits are the slow grid dimension, so CTAs whose chunk lies
+//     beyond the sequence's length (they exit at once) are scheduled last, not in between;
 //   * a cache row (D elements) is read by D*sizeof(T)/16 adjacent lanes with one 128-bit load
-//     each, so a warp instruction covers 512 contiguous bytes of the cache; K and V rows of
-//     several iterations are issued before any is consumed (memory-level parallelism is what a
-//     bandwidth-bound kernel lives on);
+//     each, so a warp instruction covers 512 contiguous bytes of the cache; a lane issues the K
+//     and V loads of 4 row groups (128 bytes) before it consumes any, and 16-24 such warps per
+//     SM keep ~100 KB in flight: memory-level parallelism is what a bandwidth-bound kernel
+//     lives on;
 //   * q.k partial sums are reduced over those lanes with warp shuffles; each lane keeps an
 //     online-softmax state (max, sum, D/lanes accumulators) for the rows it has seen;
 //   * the append is fused: the lanes that own row `len` take k_new/v_new from the token's
 //     vectors, use them, and store them into the cache;
-//   * per-CTA results go to the split-K workspace as (unnormalised out[D], max, sum) and the
-//     combine kernel merges the splits, writes out, and bumps the sequence length.
+//   * split-K merge without a second kernel and without waiting: a CTA writes (unnormalised
+//     out[D], max, sum) to the workspace, fences, and takes a ticket; whoever draws the last
+//     ticket of its (sequence, head) merges the records and writes `out`. A second ticket per
+//     sequence, taken by every CTA after it has read the length, lets the very last CTA of a
+//     sequence store length + 1. Tickets are returned to zero by their last holder, so a
+//     workspace zeroed once stays usable forever;
+//   * launched with programmatic stream serialization: the next decode call's CTAs are already
+//     resident (parked in griddepcontrol.wait) when this grid drains.
 // In direct mode (one split; the fp32 single-sequence path) the CTA normalises and writes the
 // output itself and no workspace is used.
 #include <cfloat>
@@ -25,8 +34,29 @@
 namespace dadattn {
 namespace {
 
-constexpr int kDecodeWarps = 4;
-constexpr int kDecodeUnroll = 4;
+constexpr int kDecodeWarps = 8;
+constexpr int kDecodeThreads = kDecodeWarps * 32;
+constexpr int kDecodeBatch = 4;   // row groups whose loads a lane keeps in flight
+constexpr int kMinChunk = 256;    // smallest number of cache rows a CTA is given
+constexpr int kTargetCtas = 592;  // 4 per SM: below that the cache is split across CTAs
+
+// Rows per CTA. With enough (sequence, head) pairs to fill the GPU a CTA walks a whole
+// sequence (measured fastest: no records, no tickets); with few pairs the rows are split so
+// that about kTargetCtas CTAs exist. Depends only on (B, H, max_len), so the workspace size and
+// the kernel agree.
+inline int chunk_rows(int B, int H, int max_len) {
+  const long long pairs = static_cast<long long>(B) * H;
+  long long want_splits = (kTargetCtas + pairs - 1) / pairs;
+  if (want_splits < 1) want_splits = 1;
+  long long rows = (max_len + want_splits - 1) / want_splits;
+  if (rows < kMinChunk) rows = kMinChunk;
+  rows = (rows + 127) / 128 * 128;
+  return static_cast<int>(rows);
+}
+inline int split_count(int B, int H, int max_len) {
+  const int c = chunk_rows(B, H, max_len);
+  return (max_len + c - 1) / c;
+}
 
 template <typename T>
 struct Elem;
@@ -37,7 +67,6 @@ struct Elem<float> {
     f[0] = __uint_as_float(raw.x); f[1] = __uint_as_float(raw.y);
     f[2] = __uint_as_float(raw.z); f[3] = __uint_as_float(raw.w);
   }
-  __device__ static float to_float(float x) { return x; }
   __device__ static float from_float(float x) { return x; }
 };
 template <>
@@ -51,7 +80,6 @@ struct Elem<__nv_bfloat16> {
       f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
     }
   }
-  __device__ static float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
   __device__ static __nv_bfloat16 from_float(float x) { return __float2bfloat16_rn(x); }
 };
 
@@ -63,178 +91,257 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
   return r;
 }
 
-// Workspace record per (sequence, head, split): D floats of unnormalised output, then max, sum.
+// Workspace: one ticket per (sequence, head) and one per sequence (uint32, zero between calls),
+// padded to 256 bytes, then the records [B*H][splits][D + 2] fp32 (unnormalised output, max, sum).
 __host__ __device__ inline size_t partial_stride(int D) { return static_cast<size_t>(D) + 2; }
+inline size_t record_bytes(int B, int H, int D, int max_len) {
+  const int splits = split_count(B, H, max_len);
+  return static_cast<size_t>(B) * H * splits * partial_stride(D) * sizeof(float);
+}
+inline size_t ticket_bytes(int B, int H) {
+  return (sizeof(uint32_t) * (static_cast<size_t>(B) * H + B) + 255) / 256 * 256;
+}
+inline size_t workspace_bytes(int B, int H, int D, int max_len) {
+  return ticket_bytes(B, H) + (record_bytes(B, H, D, max_len) + 255) / 256 * 256;
+}
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kDecodeWarps * 32)
-decode_splitk_kernel(T* __restrict__ out, float* __restrict__ partial, const T* __restrict__ q,
-                     const T* __restrict__ k_new, const T* __restrict__ v_new,
-                     T* __restrict__ k_cache, T* __restrict__ v_cache,
-                     const int32_t* __restrict__ lengths, int fixed_len, int H, int max_len,
-                     int chunk, float scale, int direct, int* __restrict__ status) {
+__global__ void __launch_bounds__(kDecodeThreads)
+decode_splitk_kernel(T* __restrict__ out, float* __restrict__ partial,
+                     unsigned* __restrict__ tickets, unsigned* __restrict__ seq_tickets,
+                     const T* __restrict__ q, const T* __restrict__ k_new,
+                     const T* __restrict__ v_new, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                     int32_t* __restrict__ lengths, int fixed_len, int H, int max_len, int chunk,
+                     float scale, int* __restrict__ status) {
   constexpr int EPL = Elem<T>::kPerLane;  // elements per lane (one 16-byte load)
   constexpr int LPK = D / EPL;            // lanes per cache row
   constexpr int KPI = 32 / LPK;           // cache rows per warp instruction
   static_assert(LPK >= 1 && LPK <= 32 && (LPK & (LPK - 1)) == 0, "row must split over a warp");
 
-  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int splits = gridDim.x;
-  const int len = lengths ? lengths[b] : fixed_len;  // rows already in the cache
+  // Everything this grid reads may have been written by the grid before it.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  const int bh = blockIdx.x, split = blockIdx.y, splits = gridDim.y;
+  const int b = bh / H;
+  __shared__ int sh_len, sh_last;
+  __shared__ float sh_acc[kDecodeWarps][D];
+  __shared__ float sh_m[kDecodeWarps], sh_l[kDecodeWarps];
+  if (threadIdx.x == 0) sh_len = lengths ? lengths[b] : fixed_len;  // rows already in the cache
+  __syncthreads();  // one reader per CTA: its ticket below is taken strictly after this read
+  const int len = sh_len;
   if (len < 0 || len >= max_len) {
-    if (split == 0 && h == 0 && threadIdx.x == 0) atomicExch(status, DADATTN_E_ARG);
+    if (split == 0 && bh % H == 0 && threadIdx.x == 0) atomicExch(status, DADATTN_E_ARG);
     return;
   }
   const int total = len + 1;  // rows visible to the new token, itself included
-  const int row_begin = split * chunk;
-  if (row_begin >= total) return;
-  const int row_end = min(row_begin + chunk, total);
+  const int n_active = (total + chunk - 1) / chunk;
+  const bool direct = lengths == nullptr;
 
-  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int slot = lane / LPK, part = lane % LPK;
-  const size_t vec_off = (static_cast<size_t>(b) * H + h) * D + part * EPL;
-  const size_t cache_base = (static_cast<size_t>(b) * H + h) * max_len * D + part * EPL;
+  if (split < n_active) {
+    const int row_begin = split * chunk;
+    const int row_end = min(row_begin + chunk, total);
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int slot = lane / LPK, part = lane % LPK;
+    const size_t vec_off = static_cast<size_t>(bh) * D + part * EPL;
+    const size_t cache_base = static_cast<size_t>(bh) * max_len * D + part * EPL;
 
-  float qf[EPL];
-  Elem<T>::unpack(qf, *reinterpret_cast<const uint4*>(q + vec_off));
-
-  float m = -FLT_MAX, l = 0.f, acc[EPL];
+    float qf[EPL];
+    Elem<T>::unpack(qf, *reinterpret_cast<const uint4*>(q + vec_off));
+    float m = -FLT_MAX, l = 0.f, acc[EPL];
 #pragma unroll
-  for (int e = 0; e < EPL; ++e) acc[e] = 0.f;
+    for (int e = 0; e < EPL; ++e) acc[e] = 0.f;
 
-  for (int base = row_begin + warp * KPI; base < row_end; base += kDecodeWarps * KPI * kDecodeUnroll) {
-    uint4 kr[kDecodeUnroll], vr[kDecodeUnroll];
-    bool ok[kDecodeUnroll];
+    for (int base = row_begin + warp * KPI * kDecodeBatch; base < row_end;
+         base += kDecodeWarps * KPI * kDecodeBatch) {
+      uint4 kr[kDecodeBatch], vr[kDecodeBatch];
+      bool ok[kDecodeBatch];
 #pragma unroll
-    for (int u = 0; u < kDecodeUnroll; ++u) {
-      const int row = base + u * kDecodeWarps * KPI + slot;
-      ok[u] = row < row_end;
-      kr[u] = make_uint4(0, 0, 0, 0);
-      vr[u] = make_uint4(0, 0, 0, 0);
-      if (ok[u]) {
-        if (row == len) {  // the token being appended: use its vectors and store them
-          kr[u] = *reinterpret_cast<const uint4*>(k_new + vec_off);
-          vr[u] = *reinterpret_cast<const uint4*>(v_new + vec_off);
-          *reinterpret_cast<uint4*>(k_cache + cache_base + static_cast<size_t>(row) * D) = kr[u];
-          *reinterpret_cast<uint4*>(v_cache + cache_base + static_cast<size_t>(row) * D) = vr[u];
-        } else {
-          kr[u] = ld_stream(k_cache + cache_base + static_cast<size_t>(row) * D);
-          vr[u] = ld_stream(v_cache + cache_base + static_cast<size_t>(row) * D);
+      for (int u = 0; u < kDecodeBatch; ++u) {
+        const int row = base + u * KPI + slot;
+        ok[u] = row < row_end;
+        kr[u] = make_uint4(0, 0, 0, 0);
+        vr[u] = make_uint4(0, 0, 0, 0);
+        if (ok[u]) {
+          if (row == len) {  // the token being appended: use its vectors and store them
+            kr[u] = *reinterpret_cast<const uint4*>(k_new + vec_off);
+            vr[u] = *reinterpret_cast<const uint4*>(v_new + vec_off);
+            *reinterpret_cast<uint4*>(k_cache + cache_base + static_cast<size_t>(row) * D) = kr[u];
+            *reinterpret_cast<uint4*>(v_cache + cache_base + static_cast<size_t>(row) * D) = vr[u];
+          } else {
+            kr[u] = ld_stream(k_cache + cache_base + static_cast<size_t>(row) * D);
+            vr[u] = ld_stream(v_cache + cache_base + static_cast<size_t>(row) * D);
+          }
         }
       }
+      float s[kDecodeBatch];
+      float m_new = m;
+#pragma unroll
+      for (int u = 0; u < kDecodeBatch; ++u) {
+        float kf[EPL];
+        Elem<T>::unpack(kf, kr[u]);
+        float dot = 0.f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) dot = fmaf(qf[e], kf[e], dot);
+#pragma unroll
+        for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        s[u] = ok[u] ? dot * scale : -FLT_MAX;
+        m_new = fmaxf(m_new, s[u]);
+      }
+      if (m_new > -FLT_MAX) {  // at least one row seen by this lane group so far
+        const float corr = expf(m - m_new);
+        l *= corr;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc[e] *= corr;
+#pragma unroll
+        for (int u = 0; u < kDecodeBatch; ++u) {
+          if (!ok[u]) continue;
+          const float p = expf(s[u] - m_new);
+          l += p;
+          float vf[EPL];
+          Elem<T>::unpack(vf, vr[u]);
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) acc[e] = fmaf(p, vf[e], acc[e]);
+        }
+        m = m_new;
+      }
     }
-    float s[kDecodeUnroll];
-    float m_new = m;
+
+    // Merge the KPI row slots of the warp (lanes with equal `part`), then the warps.
 #pragma unroll
-    for (int u = 0; u < kDecodeUnroll; ++u) {
-      float kf[EPL];
-      Elem<T>::unpack(kf, kr[u]);
-      float dot = 0.f;
+    for (int o = LPK; o < 32; o <<= 1) {
+      const float m_o = __shfl_xor_sync(0xffffffffu, m, o);
+      const float l_o = __shfl_xor_sync(0xffffffffu, l, o);
+      const float m_new = fmaxf(m, m_o);
+      const float ca = m > -FLT_MAX ? expf(m - m_new) : 0.f;
+      const float cb = m_o > -FLT_MAX ? expf(m_o - m_new) : 0.f;
+      l = l * ca + l_o * cb;
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) dot = fmaf(qf[e], kf[e], dot);
-#pragma unroll
-      for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      s[u] = ok[u] ? dot * scale : -FLT_MAX;
-      m_new = fmaxf(m_new, s[u]);
-    }
-    if (m_new > -FLT_MAX) {  // at least one row seen by this lane group so far
-      const float corr = expf(m - m_new);
-      l *= corr;
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) acc[e] *= corr;
-#pragma unroll
-      for (int u = 0; u < kDecodeUnroll; ++u) {
-        if (!ok[u]) continue;
-        const float p = expf(s[u] - m_new);
-        l += p;
-        float vf[EPL];
-        Elem<T>::unpack(vf, vr[u]);
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) acc[e] = fmaf(p, vf[e], acc[e]);
+      for (int e = 0; e < EPL; ++e) {
+        const float a_o = __shfl_xor_sync(0xffffffffu, acc[e], o);
+        acc[e] = acc[e] * ca + a_o * cb;
       }
       m = m_new;
     }
-  }
+    if (slot == 0) {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) sh_acc[warp][part * EPL + e] = acc[e];
+      if (part == 0) {
+        sh_m[warp] = m;
+        sh_l[warp] = l;
+      }
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < D; d += kDecodeThreads) {
+      float mm = -FLT_MAX;
+#pragma unroll
+      for (int w = 0; w < kDecodeWarps; ++w) mm = fmaxf(mm, sh_m[w]);
+      float ll = 0.f, aa = 0.f;
+#pragma unroll
+      for (int w = 0; w < kDecodeWarps; ++w) {
+        const float c = sh_m[w] > -FLT_MAX ? expf(sh_m[w] - mm) : 0.f;
+        ll += sh_l[w] * c;
+        aa += sh_acc[w][d] * c;
+      }
+      if (n_active == 1) {  // the only split of this (sequence, head): finish here
+        out[static_cast<size_t>(bh) * D + d] = Elem<T>::from_float(aa / ll);
+      } else {
+        float* rec = partial + (static_cast<size_t>(bh) * splits + split) * partial_stride(D);
+        rec[d] = aa;
+        if (d == 0) {
+          rec[D] = mm;
+          rec[D + 1] = ll;
+        }
+      }
+    }
 
-  // Merge the KPI row-slots of the warp (lanes with equal `part`), then the warps.
-#pragma unroll
-  for (int o = LPK; o < 32; o <<= 1) {
-    const float m_o = __shfl_xor_sync(0xffffffffu, m, o);
-    const float l_o = __shfl_xor_sync(0xffffffffu, l, o);
-    const float m_new = fmaxf(m, m_o);
-    const float ca = m > -FLT_MAX ? expf(m - m_new) : 0.f;
-    const float cb = m_o > -FLT_MAX ? expf(m_o - m_new) : 0.f;
-    l = l * ca + l_o * cb;
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) {
-      const float a_o = __shfl_xor_sync(0xffffffffu, acc[e], o);
-      acc[e] = acc[e] * ca + a_o * cb;
-    }
-    m = m_new;
-  }
-
-  __shared__ float sh_acc[kDecodeWarps][D];
-  __shared__ float sh_m[kDecodeWarps], sh_l[kDecodeWarps];
-  if (slot == 0) {
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) sh_acc[warp][part * EPL + e] = acc[e];
-    if (part == 0) {
-      sh_m[warp] = m;
-      sh_l[warp] = l;
-    }
-  }
-  __syncthreads();
-  for (int d = threadIdx.x; d < D; d += kDecodeWarps * 32) {
-    float mm = -FLT_MAX;
-#pragma unroll
-    for (int w = 0; w < kDecodeWarps; ++w) mm = fmaxf(mm, sh_m[w]);
-    float ll = 0.f, aa = 0.f;
-#pragma unroll
-    for (int w = 0; w < kDecodeWarps; ++w) {
-      const float c = sh_m[w] > -FLT_MAX ? expf(sh_m[w] - mm) : 0.f;
-      ll += sh_l[w] * c;
-      aa += sh_acc[w][d] * c;
-    }
-    if (direct) {
-      out[(static_cast<size_t>(b) * H + h) * D + d] = Elem<T>::from_float(aa / ll);
-    } else {
-      float* rec = partial + ((static_cast<size_t>(b) * H + h) * splits + split) * partial_stride(D);
-      rec[d] = aa;
-      if (d == 0) {
-        rec[D] = mm;
-        rec[D + 1] = ll;
+    if (n_active > 1) {
+      // Publish the record, then draw a ticket; the holder of the last one merges.
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) sh_last = (atomicAdd(&tickets[bh], 1u) == static_cast<unsigned>(n_active - 1));
+      __syncthreads();
+      if (sh_last) {
+        __threadfence();
+        const float* rec = partial + static_cast<size_t>(bh) * splits * partial_stride(D);
+        for (int d = threadIdx.x; d < D; d += kDecodeThreads) {
+          float mm = -FLT_MAX;
+          for (int s2 = 0; s2 < n_active; ++s2) mm = fmaxf(mm, __ldcg(rec + s2 * partial_stride(D) + D));
+          float ll = 0.f, aa = 0.f;
+          for (int s2 = 0; s2 < n_active; ++s2) {
+            const float* r = rec + s2 * partial_stride(D);
+            const float c = expf(__ldcg(r + D) - mm);
+            ll += __ldcg(r + D + 1) * c;
+            aa += __ldcg(r + d) * c;
+          }
+          out[static_cast<size_t>(bh) * D + d] = Elem<T>::from_float(aa / ll);
+        }
+        if (threadIdx.x == 0) tickets[bh] = 0;  // ready for the next call
       }
     }
   }
-}
 
-// Merges the split-K records of one (sequence, head), writes out, and (head 0) stores len + 1.
-template <typename T, int D>
-__global__ void decode_combine_kernel(T* __restrict__ out, const float* __restrict__ partial,
-                                      int32_t* __restrict__ lengths, int H, int max_len,
-                                      int chunk, int splits) {
-  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
-  const int len = lengths[b];
-  if (len < 0 || len >= max_len) return;
-  const int used = min(splits, (len + 1 + chunk - 1) / chunk);
-  const float* rec = partial + (static_cast<size_t>(b) * H + h) * splits * partial_stride(D);
-  float mm = -FLT_MAX;
-  for (int s = 0; s < used; ++s) mm = fmaxf(mm, rec[s * partial_stride(D) + D]);
-  float ll = 0.f, aa = 0.f;
-  for (int s = 0; s < used; ++s) {
-    const float* r = rec + s * partial_stride(D);
-    const float c = expf(r[D] - mm);
-    ll += r[D + 1] * c;
-    aa += r[d] * c;
+  // Every CTA of the sequence has read its length by the time it takes this ticket; the last
+  // one may therefore advance it.
+  if (!direct && threadIdx.x == 0) {
+    const unsigned all = static_cast<unsigned>(H) * splits;
+    if (atomicAdd(&seq_tickets[b], 1u) == all - 1) {
+      seq_tickets[b] = 0;
+      lengths[b] = len + 1;
+    }
   }
-  out[(static_cast<size_t>(b) * H + h) * D + d] = Elem<T>::from_float(aa / ll);
-  __syncthreads();
-  // Safe to bump here: every split-K CTA of this call finished before this kernel started.
-  if (h == 0 && d == 0) lengths[b] = len + 1;
 }
 
-// Rows of the cache per CTA. 128 rows = 32 per warp = 8 K + 8 V 16-byte loads in flight per lane.
-constexpr int kChunk = 128;
+// Programmatic stream serialization: the grid may be scheduled while its predecessor in the
+// stream drains; griddepcontrol.wait at the top of the kernel restores the ordering.
+template <typename Kernel, typename... Args>
+cudaError_t launch_serialized(Kernel kernel, dim3 grid, int threads, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
+template <int DH>
+int launch_decode_bf16(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
+                       const uint16_t* v_new, uint16_t* k_cache, uint16_t* v_cache,
+                       int32_t* lengths, int B, int H, int max_len, float scale,
+                       unsigned* tickets, float* partial, int* status, cudaStream_t st) {
+  using T = __nv_bfloat16;
+  const int chunk = chunk_rows(B, H, max_len);
+  const int splits = split_count(B, H, max_len);
+  unsigned* seq_tickets = tickets + static_cast<size_t>(B) * H;
+  dim3 grid(static_cast<unsigned>(B) * H, splits);
+  DAD_CUDA(launch_serialized(decode_splitk_kernel<T, DH>, grid, kDecodeThreads, st,
+                             reinterpret_cast<T*>(out), partial, tickets, seq_tickets,
+                             reinterpret_cast<const T*>(q), reinterpret_cast<const T*>(k_new),
+                             reinterpret_cast<const T*>(v_new), reinterpret_cast<T*>(k_cache),
+                             reinterpret_cast<T*>(v_cache), lengths, 0, H, max_len, chunk, scale,
+                             status));
+  return DADATTN_OK;
+}
+
+int check_decode_bf16(const void* out, const void* q, const void* k_new, const void* v_new,
+                      const void* k_cache, const void* v_cache, const void* lengths, int B, int H,
+                      int D, int max_len) {
+  if (!out || !q || !k_new || !v_new || !k_cache || !v_cache || !lengths)
+    return fail(DADATTN_E_ARG, "decode: null pointer");
+  if (B <= 0 || H <= 0 || max_len <= 0 || H > 65535 ||
+      static_cast<long long>(B) * H > 0x7fffffffLL)
+    return fail(DADATTN_E_ARG, "decode: bad sizes B=%d H=%d max_len=%d", B, H, max_len);
+  if (D != 64 && D != 128) return fail(DADATTN_E_UNSUPPORTED, "decode bf16: unsupported D %d", D);
+  if (!aligned(out, 16) || !aligned(q, 16) || !aligned(k_new, 16) || !aligned(v_new, 16) ||
+      !aligned(k_cache, 16) || !aligned(v_cache, 16))
+    return fail(DADATTN_E_ARG, "decode: pointers must be 16-byte aligned");
+  return DADATTN_OK;
+}
 
 }  // namespace
 }  // namespace dadattn
@@ -243,50 +350,30 @@ using namespace dadattn;
 
 extern "C" size_t dadattn_decode_workspace_bytes(int B, int H, int D, int max_len) {
   if (B <= 0 || H <= 0 || D <= 0 || max_len <= 0) return 0;
-  const size_t splits = (static_cast<size_t>(max_len) + kChunk - 1) / kChunk;
-  return static_cast<size_t>(B) * H * splits * partial_stride(D) * sizeof(float);
+  return workspace_bytes(B, H, D, max_len);
 }
 
 extern "C" int dadattn_decode_bf16(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
                                    const uint16_t* v_new, uint16_t* k_cache, uint16_t* v_cache,
                                    int32_t* lengths, int B, int H, int D, int max_len,
-                                   float scale, void* workspace, size_t workspace_bytes,
+                                   float scale, void* workspace, size_t workspace_bytes_given,
                                    dadattn_stream_t stream) {
-  if (!out || !q || !k_new || !v_new || !k_cache || !v_cache || !lengths || !workspace)
-    return fail(DADATTN_E_ARG, "decode: null pointer");
-  if (B <= 0 || H <= 0 || max_len <= 0 || B > 65535 || H > 65535)
-    return fail(DADATTN_E_ARG, "decode: bad sizes B=%d H=%d max_len=%d", B, H, max_len);
-  if (D != 64 && D != 128) return fail(DADATTN_E_UNSUPPORTED, "decode bf16: unsupported D %d", D);
-  if (!aligned(out, 16) || !aligned(q, 16) || !aligned(k_new, 16) || !aligned(v_new, 16) ||
-      !aligned(k_cache, 16) || !aligned(v_cache, 16) || !aligned(workspace, 16))
-    return fail(DADATTN_E_ARG, "decode: pointers must be 16-byte aligned");
-  if (workspace_bytes < dadattn_decode_workspace_bytes(B, H, D, max_len))
-    return fail(DADATTN_E_WORKSPACE, "decode: workspace %zu < %zu bytes", workspace_bytes,
-                dadattn_decode_workspace_bytes(B, H, D, max_len));
+  if (int rc = check_decode_bf16(out, q, k_new, v_new, k_cache, v_cache, lengths, B, H, D, max_len))
+    return rc;
+  if (!workspace || !aligned(workspace, 16))
+    return fail(DADATTN_E_ARG, "decode: workspace must be a 16-byte aligned device pointer");
+  if (workspace_bytes_given < workspace_bytes(B, H, D, max_len))
+    return fail(DADATTN_E_WORKSPACE, "decode: workspace %zu < %zu bytes", workspace_bytes_given,
+                workspace_bytes(B, H, D, max_len));
   int* status = device_status_word();
   if (!status) return DADATTN_E_CUDA;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int splits = (max_len + kChunk - 1) / kChunk;
-  using T = __nv_bfloat16;
-  dim3 grid(splits, H, B), cgrid(H, B);
-  float* partial = static_cast<float*>(workspace);
-#define DAD_DECODE(DH)                                                                          \
-  decode_splitk_kernel<T, DH><<<grid, kDecodeWarps * 32, 0, st>>>(                              \
-      reinterpret_cast<T*>(out), partial, reinterpret_cast<const T*>(q),                        \
-      reinterpret_cast<const T*>(k_new), reinterpret_cast<const T*>(v_new),                     \
-      reinterpret_cast<T*>(k_cache), reinterpret_cast<T*>(v_cache), lengths, 0, H, max_len,     \
-      kChunk, scale, 0, status);                                           \
-  DAD_LAUNCH_CHECK("decode_splitk_kernel");                                                     \
-  decode_combine_kernel<T, DH><<<cgrid, DH, 0, st>>>(reinterpret_cast<T*>(out), partial,        \
-                                                     lengths, H, max_len, kChunk, splits);      \
-  DAD_LAUNCH_CHECK("decode_combine_kernel");
-  if (D == 64) {
-    DAD_DECODE(64)
-  } else {
-    DAD_DECODE(128)
-  }
-#undef DAD_DECODE
-  return DADATTN_OK;
+  unsigned* tickets = static_cast<unsigned*>(workspace);
+  float* partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + ticket_bytes(B, H));
+  return D == 64 ? launch_decode_bf16<64>(out, q, k_new, v_new, k_cache, v_cache, lengths, B, H,
+                                          max_len, scale, tickets, partial, status, st)
+                 : launch_decode_bf16<128>(out, q, k_new, v_new, k_cache, v_cache, lengths, B, H,
+                                           max_len, scale, tickets, partial, status, st);
 }
 
 extern "C" int dadattn_decode_f32(float* out, const float* q, const float* k_new,
@@ -306,18 +393,19 @@ extern "C" int dadattn_decode_f32(float* out, const float* q, const float* k_new
   int* status = device_status_word();
   if (!status) return DADATTN_E_CUDA;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  dim3 grid(1, H, 1);
+  dim3 grid(H, 1);  // one CTA per head walks the whole cache: direct mode, no workspace
 #define DAD_DECODE32(DH)                                                                        \
   case DH:                                                                                      \
-    decode_splitk_kernel<float, DH><<<grid, kDecodeWarps * 32, 0, st>>>(                        \
-        out, nullptr, q, k_new, v_new, k_cache, v_cache, nullptr, pos, H, max_len, max_len,     \
-        scale, 1, status);                                                                      \
+    DAD_CUDA(launch_serialized(decode_splitk_kernel<float, DH>, grid, kDecodeThreads, st, out,  \
+                               static_cast<float*>(nullptr), static_cast<unsigned*>(nullptr),   \
+                               static_cast<unsigned*>(nullptr), q, k_new, v_new, k_cache,       \
+                               v_cache, static_cast<int32_t*>(nullptr), pos, H, max_len,        \
+                               max_len, scale, status));                                        \
     break;
   switch (D) {
     DAD_DECODE32(16) DAD_DECODE32(32) DAD_DECODE32(64) DAD_DECODE32(128)
   }
 #undef DAD_DECODE32
-  DAD_LAUNCH_CHECK("decode_splitk_kernel<float>");
   return DADATTN_OK;
 }
 
@@ -329,16 +417,21 @@ extern "C" int dadattn_decode_f32(float* out, const float* q, const float* k_new
 // for a later cudaMalloc; a latency-critical decode loop cannot afford the device-wide
 // synchronisation an allocation implies; and DadGPT itself sizes all of its buffers once, in
 // model_alloc / kv_cache_alloc, and never allocates inside generate_tokens. For such callers the
-// split-K partials live in the fixed array below instead of a caller-provided workspace, and
-// the bad-length report goes to a fixed word instead of the lazily allocated status word.
+// split-K tickets and records live in the fixed array below instead of a caller-provided
+// workspace, and the bad-length report goes to a fixed word instead of the lazily allocated
+// status word.
 //
 // The array is part of the library image: every GPU that loads libdadattn.so holds these
-// 8 MiB until the process exits, whether or not this entry point is ever called.
+// 8 MiB until the process exits, whether or not this entry point is ever called. Its first
+// 64 KiB are the tickets, at a fixed place whatever the shape of a call: they are zero when the
+// module is loaded and every call returns them to zero, which is the only state a call needs
+// from its predecessors. The records behind them are written before they are read.
 // ---------------------------------------------------------------------------------------------
 namespace dadattn {
 namespace {
 
 constexpr size_t kNoAllocScratchBytes = size_t(8) << 20;
+constexpr size_t kNoAllocTicketBytes = size_t(64) << 10;
 static __device__ __align__(256) unsigned char g_decode_scratch[kNoAllocScratchBytes];
 static __device__ int g_decode_noalloc_status;
 
@@ -367,26 +460,6 @@ int noalloc_setup(float** scratch, int** status) {
   return DADATTN_OK;
 }
 
-template <int DH>
-int launch_decode_noalloc(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
-                          const uint16_t* v_new, uint16_t* k_cache, uint16_t* v_cache,
-                          int32_t* lengths, int B, int H, int max_len, float scale,
-                          float* partial, int* status, cudaStream_t st) {
-  using T = __nv_bfloat16;
-  const int splits = (max_len + kChunk - 1) / kChunk;
-  dim3 grid(splits, H, B), cgrid(H, B);
-  decode_splitk_kernel<T, DH><<<grid, kDecodeWarps * 32, 0, st>>>(
-      reinterpret_cast<T*>(out), partial, reinterpret_cast<const T*>(q),
-      reinterpret_cast<const T*>(k_new), reinterpret_cast<const T*>(v_new),
-      reinterpret_cast<T*>(k_cache), reinterpret_cast<T*>(v_cache), lengths, 0, H, max_len, kChunk,
-      scale, 0, status);
-  DAD_LAUNCH_CHECK("decode_splitk_kernel (no-alloc)");
-  decode_combine_kernel<T, DH><<<cgrid, DH, 0, st>>>(reinterpret_cast<T*>(out), partial, lengths,
-                                                     H, max_len, kChunk, splits);
-  DAD_LAUNCH_CHECK("decode_combine_kernel (no-alloc)");
-  return DADATTN_OK;
-}
-
 }  // namespace
 }  // namespace dadattn
 
@@ -395,26 +468,23 @@ extern "C" int dadattn_decode_bf16_noalloc(uint16_t* out, const uint16_t* q,
                                            uint16_t* k_cache, uint16_t* v_cache, int32_t* lengths,
                                            int B, int H, int D, int max_len, float scale,
                                            dadattn_stream_t stream) {
-  if (!out || !q || !k_new || !v_new || !k_cache || !v_cache || !lengths)
-    return fail(DADATTN_E_ARG, "decode: null pointer");
-  if (B <= 0 || H <= 0 || max_len <= 0 || B > 65535 || H > 65535)
-    return fail(DADATTN_E_ARG, "decode: bad sizes B=%d H=%d max_len=%d", B, H, max_len);
-  if (D != 64 && D != 128) return fail(DADATTN_E_UNSUPPORTED, "decode bf16: unsupported D %d", D);
-  if (!aligned(out, 16) || !aligned(q, 16) || !aligned(k_new, 16) || !aligned(v_new, 16) ||
-      !aligned(k_cache, 16) || !aligned(v_cache, 16))
-    return fail(DADATTN_E_ARG, "decode: pointers must be 16-byte aligned");
+  if (int rc = check_decode_bf16(out, q, k_new, v_new, k_cache, v_cache, lengths, B, H, D, max_len))
+    return rc;
   const size_t need = dadattn_decode_workspace_bytes(B, H, D, max_len);
-  if (need > kNoAllocScratchBytes)
+  if (need > kNoAllocScratchBytes || ticket_bytes(B, H) > kNoAllocTicketBytes ||
+      record_bytes(B, H, D, max_len) > kNoAllocScratchBytes - kNoAllocTicketBytes)
     return fail(DADATTN_E_WORKSPACE,
                 "decode (no-alloc): B=%d H=%d D=%d max_len=%d needs %zu bytes of split-K scratch, "
                 "the built-in array holds %zu; use dadattn_decode_bf16 with your own workspace",
                 B, H, D, max_len, need, static_cast<size_t>(kNoAllocScratchBytes));
-  float* partial = nullptr;
+  float* scratch = nullptr;
   int* status = nullptr;
-  if (int rc = noalloc_setup(&partial, &status)) return rc;
+  if (int rc = noalloc_setup(&scratch, &status)) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return D == 64 ? launch_decode_noalloc<64>(out, q, k_new, v_new, k_cache, v_cache, lengths, B, H,
-                                             max_len, scale, partial, status, st)
-                 : launch_decode_noalloc<128>(out, q, k_new, v_new, k_cache, v_cache, lengths, B,
-                                              H, max_len, scale, partial, status, st);
+  unsigned* tickets = reinterpret_cast<unsigned*>(scratch);
+  float* partial = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + kNoAllocTicketBytes);
+  return D == 64 ? launch_decode_bf16<64>(out, q, k_new, v_new, k_cache, v_cache, lengths, B, H,
+                                          max_len, scale, tickets, partial, status, st)
+                 : launch_decode_bf16<128>(out, q, k_new, v_new, k_cache, v_cache, lengths, B, H,
+                                           max_len, scale, tickets, partial, status, st);
 }

@@ -129,8 +129,11 @@ int dadattn_decode_f32(float* out, const float* q, const float* k_new, const flo
  * Caches: [B,H,max_len,D] bf16. lengths[B] (int32, device) holds each sequence's current length
  * L_b; the call writes k_new,v_new [B,H,D] at row L_b, attends over rows 0..L_b, and stores
  * L_b + 1 back. Sequences with L_b >= max_len are left untouched and reported through
- * DADATTN_E_ARG at the next dadattn_device_status(). workspace: split-K partials, at least
- * dadattn_decode_workspace_bytes() bytes, 256-byte aligned. */
+ * DADATTN_E_ARG at the next dadattn_device_status(). workspace: split-K tickets and records, at
+ * least dadattn_decode_workspace_bytes() bytes, 16-byte aligned. It must be zero-filled
+ * (cudaMemset) before its first use and again whenever B, H or max_len change; between calls of
+ * one shape the library leaves it in a reusable state. Two calls that share a workspace must not
+ * overlap on the GPU. */
 size_t dadattn_decode_workspace_bytes(int B, int H, int D, int max_len);
 int dadattn_decode_bf16(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
                         const uint16_t* v_new, uint16_t* k_cache, uint16_t* v_cache,
@@ -145,13 +148,16 @@ int dadattn_decode_bf16(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
  * workspace: the split-K partials go to a fixed 8 MiB array inside the library image (held by
  * every GPU that loads the library, until exit). The call performs no cudaMalloc/cudaFree and
  * uses no allocating routine.
- *  - Limit: dadattn_decode_workspace_bytes(B,H,D,max_len) must be <= 8 MiB (8388608 bytes),
- *    e.g. B*H <= 3177 at max_len 1280, D 64; larger shapes return DADATTN_E_WORKSPACE.
+ *  - Limit: the array is 8 MiB (8388608 bytes): 64 KiB of split-K tickets (B*H + B <= 16384)
+ *    and the rest for records (none when B*H >= 592, where each CTA walks a whole sequence);
+ *    dadattn_decode_workspace_bytes(B,H,D,max_len) tells what a shape needs, and shapes that
+ *    need more than the array holds return DADATTN_E_WORKSPACE.
  *  - The first call on each device looks up the array's device address
  *    (cudaGetSymbolAddress); make that first call before starting any stream capture.
- *  - All calls share the one array and it keeps the previous call's partials. Nothing in it has
- *    to start at zero (every record is written before it is read within a call), but two calls
- *    that overlap on the GPU (different streams, or threads) race on it: serialise them.
+ *  - All calls share the one array and it keeps the previous call's contents. Only the tickets
+ *    have to be zero when a call starts: they are zero when the library is loaded and every call
+ *    hands them back zeroed (records are written before they are read within a call). Two calls
+ *    that overlap on the GPU (different streams, or threads) race on the array: serialise them.
  *  - A sequence already at max_len is skipped as in dadattn_decode_bf16, but this variant has
  *    nowhere to report it (dadattn_device_status belongs to the allocating calls). */
 int dadattn_decode_bf16_noalloc(uint16_t* out, const uint16_t* q, const uint16_t* k_new,

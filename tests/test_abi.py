@@ -36,7 +36,10 @@ def test_no_compute_without_device_but_arguments_are_checked(lib):
     assert rc == -2 and b"unsupported d_head 48" in lib.dadattn_last_error()
     rc = lib.dadattn_decode_f32(16, 16, 16, 16, 16, 16, 4, 32, 64, 32, 0.125, None)
     assert rc == -1 and b"outside context length" in lib.dadattn_last_error()
-    assert lib.dadattn_decode_workspace_bytes(64, 12, 64, 1280) == 64 * 12 * 10 * 66 * 4
+    # tickets (B*H + B uint32, padded to 256) + records [B*H][splits][D+2] fp32; 768 pairs fill
+    # the GPU, so a CTA walks a whole sequence (1 split); 8 pairs get their rows split
+    assert lib.dadattn_decode_workspace_bytes(64, 12, 64, 1280) == 3328 + 64 * 12 * 1 * 66 * 4
+    assert lib.dadattn_decode_workspace_bytes(2, 4, 64, 1280) == 256 + 2 * 4 * 5 * 66 * 4
 
 
 def test_gpuops_shim_defines_the_reference_symbols():

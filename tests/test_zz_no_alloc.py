@@ -30,7 +30,7 @@ def test_noalloc_decode_matches_workspace_decode_twice_in_a_row(cuda):
     k1, v1, n1 = _state(cuda, B, H, L, D, lens, 1)
     k2, v2, n2 = k1.clone(), v1.clone(), n1.clone()
     ws_bytes = lib.dadattn_decode_workspace_bytes(B, H, D, L)
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=cuda)
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=cuda)
     g = torch.Generator(device=cuda).manual_seed(7)
     for call in range(2):  # the second call finds the first call's partials in the array
         q, kn, vn = (torch.randn(B, H, D, device=cuda, generator=g).to(torch.bfloat16) for _ in range(3))
@@ -53,7 +53,7 @@ def test_noalloc_decode_matches_workspace_decode_twice_in_a_row(cuda):
 
 def test_noalloc_decode_rejects_shapes_beyond_its_array(cuda):
     lib = _lib.load()
-    B, H, L, D = 4096, 12, 1280, 64  # needs ~130 MB of partials, the array holds 8 MiB
+    B, H, L, D = 4096, 12, 1280, 64  # needs ~65 MB of records, the array holds 8 MiB
     assert lib.dadattn_decode_workspace_bytes(B, H, D, L) > (8 << 20)
     x = torch.zeros(16, dtype=torch.bfloat16, device=cuda)
     n = torch.zeros(B, dtype=torch.int32, device=cuda)
