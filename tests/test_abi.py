@@ -39,7 +39,7 @@ def test_no_compute_without_device_but_arguments_are_checked(lib):
     # tickets (B*H + B uint32, padded to 256) + records [B*H][splits][D+2] fp32; 768 pairs fill
     # the GPU, so a CTA walks a whole sequence (1 split); 8 pairs get their rows split
     assert lib.dadattn_decode_workspace_bytes(64, 12, 64, 1280) == 3328 + 64 * 12 * 1 * 66 * 4
-    assert lib.dadattn_decode_workspace_bytes(2, 4, 64, 1280) == 256 + 2 * 4 * 5 * 66 * 4
+    assert lib.dadattn_decode_workspace_bytes(2, 4, 64, 1280) == 256 + 10752  # 8*5*66*4 padded to 256
 
 
 def test_gpuops_shim_defines_the_reference_symbols():
