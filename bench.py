@@ -248,7 +248,7 @@ def run_ours(args):
 
     # ---- headline: fwd + bwd, inputs resident in HBM, with per-kernel stage events ----
     import ctypes
-    stage_ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(K)]
+    stage_ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(K)]
 
     def step_resident(s, record=None):
         i = s % n_sets
@@ -256,8 +256,8 @@ def run_ours(args):
             record[0].record()
         fwd(i)
         if record is not None:
-            arr = (ctypes.c_void_p * 4)(*[e.cuda_event for e in record[1:]])
-            lib.dadattn_set_stage_events(arr, 4)
+            arr = (ctypes.c_void_p * 3)(*[e.cuda_event for e in record[1:]])
+            lib.dadattn_set_stage_events(arr, 3)
         bwd(i)
         if record is not None:
             lib.dadattn_set_stage_events(None, 0)
@@ -298,15 +298,16 @@ def run_ours(args):
         raise RuntimeError(f"device status {status} after the timed region")
     value = (f_flops + b_flops) * world / (ms_step * 1e-3) / 1e12
 
-    st = np.array([[evs[j].elapsed_time(evs[j + 1]) for j in range(4)] for evs in stage_ev])
-    ms_fwd, ms_delta, ms_dkdv, ms_dq = (float(x) for x in st.mean(axis=0))
+    # events: before fwd | before dQ (+delta) kernel | before dK/dV kernel | after it
+    st = np.array([[evs[j].elapsed_time(evs[j + 1]) for j in range(3)] for evs in stage_ev])
+    ms_fwd, ms_dq, ms_dkdv = (float(x) for x in st.mean(axis=0))
 
     if args.quick:  # profiling aid: only the headline region above, nothing else is launched
         if rank == 0:
             print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "quick": True,
                               "ms_per_step": ms_step, "steps": K, "warmup": Wm,
-                              "kernels_ms": {"fwd": ms_fwd, "delta": ms_delta, "dkdv": ms_dkdv,
-                                             "dq": ms_dq}}), flush=True)
+                              "kernels_ms": {"fwd": ms_fwd, "dq": ms_dq, "dkdv": ms_dkdv}}),
+                  flush=True)
         if world > 1:
             dist.destroy_process_group()
         return
@@ -359,8 +360,7 @@ def run_ours(args):
         "peak_source": f"{peaks['_source']} bf16_tflops (burst: the timed region lasts milliseconds)",
         "traffic": NCU_TRAFFIC_BYTES["flash_bwd_bf16_kernel<dkdv>"],
         "ms_per_launch": ms_dkdv,
-        "other_kernels_ms": {"flash_fwd_bf16_kernel": ms_fwd, "flash_delta_bf16_kernel": ms_delta,
-                             "flash_bwd_bf16_kernel<dq>": ms_dq},
+        "other_kernels_ms": {"flash_fwd_bf16_kernel": ms_fwd, "flash_bwd_bf16_kernel<dq>": ms_dq},
     }
 
     cpu_baseline = None
@@ -389,13 +389,12 @@ def run_ours(args):
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": 4 * K,
+            "gpu_launches": 3 * K,
             "roofline": roofline,
             "cpu_baseline": cpu_baseline,
             "fwd_only": {"ms": ms_fwd_only, "tflops": f_flops * world / ms_fwd_only / 1e9,
                          "hbm_gbs": f_bytes * world / ms_fwd_only / 1e6, **shorter},
-            "bwd_only": {"ms": ms_delta + ms_dkdv + ms_dq,
-                         "tflops": b_flops / (ms_delta + ms_dkdv + ms_dq) / 1e9},
+            "bwd_only": {"ms": ms_dkdv + ms_dq, "tflops": b_flops / (ms_dkdv + ms_dq) / 1e9},
             "dropout_0p1": {"ms_per_step": ms_drop,
                             "tflops": (f_flops + b_flops) * world / ms_drop / 1e9,
                             "note": "bit-exact Philox mask regenerated in every kernel"},
@@ -464,7 +463,7 @@ def bench_decode(dad, W, dev, world, barrier, max_over_ranks, torch, steps=None,
     return {"metric": "kv_decode_hbm_gbs", "value": gbs, "unit": "GB/s", "ms_total": ms,
             "steps": cfg.steps, "layers": cfg.layers, "sequences_per_gpu": cfg.B,
             "algorithmic_gb": total / 1e9, "frac_of_hbm_peak": gbs / world / float(peaks["hbm_gbs"]),
-            "peak_source": peaks["_source"], "gpu_launches": 2 * cfg.layers * cfg.steps,
+            "peak_source": peaks["_source"], "gpu_launches": cfg.layers * cfg.steps,
             "lengths_advanced": ok, "workload": cfg.name}
 
 

@@ -1,7 +1,8 @@
 // bf16 fused causal attention backward for sm_100a (tcgen05 / TMEM / TMA).
 //
-// Same decomposition as the reference's backward (cuda/attention.cu:215-228): a delta pre-pass,
-// one kernel that owns key tiles and produces dK/dV, one that owns query tiles and produces dQ.
+// Same decomposition as the reference's backward (cuda/attention.cu:215-228): one kernel that
+// owns query tiles and produces dQ (and, on the way, the reference's delta pre-pass), one that
+// owns key tiles and produces dK/dV.
 // Nothing is accumulated across CTAs, so there are no atomics and results are deterministic,
 // as in the reference. Both tensor-core kernels are one template:
 //
@@ -72,31 +73,6 @@ struct BwdBars {
   int abort_flag;
 };
 
-// delta[r] = sum_d dO[r,d] * O[r,d]; 8 bf16 per lane, D/8 lanes per row.
-template <int D>
-__global__ void flash_delta_bf16_kernel(float* __restrict__ delta,
-                                        const __nv_bfloat16* __restrict__ dout,
-                                        const __nv_bfloat16* __restrict__ out, int64_t rows) {
-  constexpr int L = D / 8;
-  const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int64_t r = t / L;
-  const int c = static_cast<int>(t % L) * 8;
-  float sum = 0.f;
-  if (r < rows) {
-    const uint4 a = *reinterpret_cast<const uint4*>(dout + r * D + c);
-    const uint4 b = *reinterpret_cast<const uint4*>(out + r * D + c);
-    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      sum = fmaf(__uint_as_float(aw[i] << 16), __uint_as_float(bw[i] << 16), sum);
-      sum = fmaf(__uint_as_float(aw[i] & 0xffff0000u), __uint_as_float(bw[i] & 0xffff0000u), sum);
-    }
-  }
-#pragma unroll
-  for (int o = L / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  if (r < rows && c == 0) delta[r] = sum;
-}
-
 // KV = true: dK/dV kernel (grid.x = key tile). KV = false: dQ kernel (grid.x = query tile).
 template <int D, bool KV, bool DROP>
 __global__ void __launch_bounds__(kBwdThreads, D == 64 ? 2 : 1)
@@ -105,8 +81,9 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
                       const __grid_constant__ CUtensorMap map_c1,
                       const __grid_constant__ CUtensorMap map_c2,
                       __nv_bfloat16* __restrict__ out1, __nv_bfloat16* __restrict__ out2,
-                      const float* __restrict__ lse, const float* __restrict__ delta, int S,
-                      float scale, float rate, PhiloxKey rng, int64_t unit0,
+                      const float* __restrict__ lse, float* __restrict__ delta,
+                      const __nv_bfloat16* __restrict__ g_out, const __nv_bfloat16* __restrict__ g_dout,
+                      int S, float scale, float rate, PhiloxKey rng, int64_t unit0,
                       int* __restrict__ status) {
   using L = BwdSmem<D, KV>;
   constexpr int kPanels = L::kPanels;
@@ -285,7 +262,26 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
     float row_lse2 = 0.f, row_delta = 0.f;
     if (!KV) {  // per-row scalars; rows beyond S contribute nothing (p = exp2(-inf) = 0)
       row_lse2 = grow < S ? lse[vec_base + grow] * kLog2e : INFINITY;
-      row_delta = grow < S ? delta[vec_base + grow] : 0.f;
+      // delta[r] = sum_d dO[r,d] * O[r,d] (the reference's flash_delta_kernel,
+      // cuda/attention.cu:76-85) is formed here, by the threads that own row r, and left in
+      // `delta` for the dK/dV kernel, which is launched after this one.
+      if (grow < S) {
+        const uint4* po = reinterpret_cast<const uint4*>(g_out + (vec_base + grow) * D);
+        const uint4* pd = reinterpret_cast<const uint4*>(g_dout + (vec_base + grow) * D);
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) {
+          const uint4 a = po[c], b2 = pd[c];
+          const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b2.x, b2.y, b2.z, b2.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            s4[i] = fmaf(__uint_as_float(aw[i] << 16), __uint_as_float(bw[i] << 16), s4[i]);
+            s4[i] = fmaf(__uint_as_float(aw[i] & 0xffff0000u), __uint_as_float(bw[i] & 0xffff0000u), s4[i]);
+          }
+        }
+        row_delta = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+        if (half == 0) delta[vec_base + grow] = row_delta;
+      }
     }
     bool ok = true;
     DAD_TRACE_DECL;
@@ -443,33 +439,29 @@ int launch_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, float* delta, cons
   if (!status) return DADATTN_E_CUDA;
   using BF = __nv_bfloat16;
 
-  stage_event(0, st);
-  const int64_t rows = static_cast<int64_t>(BH) * S;
-  const int64_t threads = rows * (D / 8);
-  flash_delta_bf16_kernel<D><<<static_cast<unsigned>((threads + 255) / 256), 256, 0, st>>>(
-      delta, reinterpret_cast<const BF*>(dout), reinterpret_cast<const BF*>(out), rows);
-  DAD_LAUNCH_CHECK("flash_delta_bf16_kernel");
-  stage_event(1, st);
-
   const PhiloxKey rng = make_philox(seed, offset);
   dim3 grid((S + kTileRows - 1) / kTileRows, BH);
-  auto kkv = flash_bwd_bf16_kernel<D, true, DROP>;
-  DAD_CUDA(cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                BwdSmem<D, true>::kBytes));
-  kkv<<<grid, kBwdThreads, BwdSmem<D, true>::kBytes, st>>>(mk, mv, mq_s, mdo_s, reinterpret_cast<BF*>(dv),
-                                                    reinterpret_cast<BF*>(dk), lse, delta, S,
-                                                    scale, rate, rng, unit0, status);
-  DAD_LAUNCH_CHECK("flash_bwd_bf16_kernel<dkdv>");
-  stage_event(2, st);
 
+  // dQ first: it also produces delta [BH,S], which the dK/dV kernel then reads.
+  stage_event(0, st);
   auto kq = flash_bwd_bf16_kernel<D, false, DROP>;
   DAD_CUDA(cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 BwdSmem<D, false>::kBytes));
-  kq<<<grid, kBwdThreads, BwdSmem<D, false>::kBytes, st>>>(mq, mdo, mk_s, mv_s, reinterpret_cast<BF*>(dq),
-                                                   nullptr, lse, delta, S, scale, rate, rng, unit0,
-                                                   status);
+  kq<<<grid, kBwdThreads, BwdSmem<D, false>::kBytes, st>>>(
+      mq, mdo, mk_s, mv_s, reinterpret_cast<BF*>(dq), nullptr, lse, delta,
+      reinterpret_cast<const BF*>(out), reinterpret_cast<const BF*>(dout), S, scale, rate, rng, unit0,
+      status);
   DAD_LAUNCH_CHECK("flash_bwd_bf16_kernel<dq>");
-  stage_event(3, st);
+  stage_event(1, st);
+
+  auto kkv = flash_bwd_bf16_kernel<D, true, DROP>;
+  DAD_CUDA(cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                BwdSmem<D, true>::kBytes));
+  kkv<<<grid, kBwdThreads, BwdSmem<D, true>::kBytes, st>>>(
+      mk, mv, mq_s, mdo_s, reinterpret_cast<BF*>(dv), reinterpret_cast<BF*>(dk), lse, delta, nullptr,
+      nullptr, S, scale, rate, rng, unit0, status);
+  DAD_LAUNCH_CHECK("flash_bwd_bf16_kernel<dkdv>");
+  stage_event(2, st);
   return DADATTN_OK;
 }
 

@@ -109,8 +109,8 @@ int dadattn_flash_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* works
 
 /* Measurement aid (no counterpart in the reference): when `events` (an array of `count`
  * cudaEvent_t) is set for the calling thread, dadattn_flash_bwd_bf16 records events[0] before
- * its delta kernel, [1] before the dK/dV kernel, [2] before the dQ kernel and [3] after it, on
- * the call's stream. Pass NULL to switch it off. */
+ * its dQ kernel (which also forms delta), [1] before the dK/dV kernel and [2] after it, on the
+ * call's stream. Pass NULL to switch it off. */
 int dadattn_set_stage_events(void** events, int count);
 
 /* ---- KV-cache decode --------------------------------------------------------------------- */
