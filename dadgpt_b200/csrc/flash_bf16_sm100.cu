@@ -93,13 +93,16 @@ struct FwdSmem {
   static constexpr int kK = kQ + kPanels * kPanelBytes;
   static constexpr int kV = kK + kStages * kPanels * kPanelBytes;
   static constexpr int kP = kV + kStages * kPanels * kPanelBytes;
-  static constexpr int kBars = kP + 2 * kPanelBytes;
+  // P tile buffers: two at D = 128 (one CTA per SM has the room), so the softmax of tile j
+  // never waits for P_{j-1} V_{j-1} to release the buffer; one at D = 64 (two CTAs per SM).
+  static constexpr int kPBufs = D == 128 ? 2 : 1;
+  static constexpr int kBars = kP + kPBufs * 2 * kPanelBytes;
   static constexpr int kBytes = kBars + 256;
 };
 
 struct FwdBars {
   uint64_t q_full, k_full[kStages], v_full[kStages], k_empty[kStages], v_empty[kStages];
-  uint64_t s_full[2], s_free[2], p_full, o_done, stat_full;
+  uint64_t s_full[2], s_free[2], p_full, o_done[2], stat_full;  // P_j V_j commits to o_done[j & 1]
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -148,7 +151,8 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(&bars->s_free[b], kSoftmaxThreads);
     }
     mbar_init(&bars->p_full, kSoftmaxThreads);
-    mbar_init(&bars->o_done, 1);
+    mbar_init(&bars->o_done[0], 1);
+    mbar_init(&bars->o_done[1], 1);
     mbar_init(&bars->stat_full, kSoftmaxThreads);
     bars->abort_flag = 0;
     fence_mbar_init();
@@ -213,14 +217,15 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
           for (int pn = 0; pn < kPanels; ++pn) {
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
-              mma_ss(tmem + kColO + h * D + pn * 64, desc_at(p_desc, h * kPanelBytes + kk * 32),
+              mma_ss(tmem + kColO + h * D + pn * 64,
+                     desc_at(p_desc, (i % L::kPBufs) * 2 * kPanelBytes + h * kPanelBytes + kk * 32),
                      desc_at(v_desc, pn * kPanelBytes + (h * 4 + kk) * 2048), idesc_o,
                      (i > 0 || kk > 0) ? 1u : 0u);
             }
           }
         }
         mma_commit(&bars->v_empty[s]);
-        mma_commit(&bars->o_done);
+        mma_commit(&bars->o_done[i & 1]);
         DAD_TRACE(1);
         return true;
       };
@@ -257,7 +262,9 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
     const uint32_t tO = tlane + kColO + half * D;  // this half's output accumulator
     const float scale_log2 = scale * kLog2e;
     const float keep_scale = DROP ? 1.0f / (1.0f - rate) : 1.0f;
-    uint8_t* p_row = smem + L::kP + half * kPanelBytes + row * 128;
+    uint8_t* p_row0 = smem + L::kP + half * kPanelBytes + row * 128;
+    // waits for P_i V_i (tile i) to have completed
+    auto wait_pv = [&](int i) { return mbar_wait(&bars->o_done[i & 1], (i >> 1) & 1, abort_flag); };
     float m = -INFINITY, l = 0.f;  // running max (log2 units, scaled) and sum of this half-row
     bool ok = true;
     DAD_TRACE_DECL;
@@ -296,7 +303,7 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
       if (j == 0) {
         m = mx;  // O is first written by an MMA with accumulate = 0: nothing to rescale
       } else if (__any_sync(0xffffffffu, mx > m + kRescaleThreshold)) {
-        if (!(ok = mbar_wait(&bars->o_done, (j - 1) & 1, abort_flag))) break;
+        if (!(ok = wait_pv(j - 1))) break;
         waited_o = true;
         tc_fence_after_sync();
         const float m_new = fmaxf(m, mx);
@@ -315,8 +322,9 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
         l *= corr;
         m = m_new;
       }
-      // P_{j-1} must have been consumed by its MMA before the buffer is overwritten
-      if (j > 0 && !waited_o && !(ok = mbar_wait(&bars->o_done, (j - 1) & 1, abort_flag))) break;
+      // The MMA that read this P buffer last (tile j - kPBufs) must have completed
+      if (j >= L::kPBufs && !(L::kPBufs == 1 && waited_o) && !(ok = wait_pv(j - L::kPBufs))) break;
+      uint8_t* p_row = p_row0 + (j % L::kPBufs) * 2 * kPanelBytes;
       if (warp == 2) DAD_TRACE(0);
 
       // ---- pass 2: p = exp2(s * scale * log2e - m), one FFMA + one MUFU per score; bf16 P goes
@@ -380,7 +388,7 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
       stat[half * 128 + row] = make_float2(m, l);
       mbar_arrive(&bars->stat_full);
       ok = mbar_wait(&bars->stat_full, 0, abort_flag) &&
-           mbar_wait(&bars->o_done, (n_kv - 1) & 1, abort_flag);
+           wait_pv(n_kv - 1);
     }
     if (ok) {
       tc_fence_after_sync();
