@@ -280,22 +280,35 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
       const bool diagonal = (j == n_kv - 1);
       const int limit = r - c0;
 
-      // ---- pass 1: max of the raw scores (scale > 0 commutes with max); both 32-column TMEM
-      // loads are in flight together. ----
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-      {
-        uint32_t x[64];
-        tmem_ld32(tS, *reinterpret_cast<uint32_t(*)[32]>(&x[0]));
-        tmem_ld32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&x[32]));
+      // The thread's 64 scores are read from TMEM (both 32-column loads in flight together).
+      // At D = 128 (registers to spare) they stay in registers for the max and for the
+      // exponentials and S is handed back to the MMA warp at once; at D = 64 (two CTAs per SM,
+      // 96 registers) they are read a second time after the max instead of being kept.
+      constexpr bool kKeepScores = (D == 128);
+      uint32_t xa[32], xb[32];
+      auto load_scores = [&]() {
+        tmem_ld32(tS, xa);
+        tmem_ld32(tS + 32, xb);
         tmem_wait_ld();
         if (diagonal) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i)
-            if (i > limit) x[i] = 0xff800000u;  // -inf
+          for (int i = 0; i < 32; ++i) {
+            if (i > limit) xa[i] = 0xff800000u;  // -inf
+            if (32 + i > limit) xb[i] = 0xff800000u;
+          }
         }
+      };
+      auto release_scores = [&]() {  // S is in registers: the next QK^T may overwrite it
+        tc_fence_before_sync();
+        mbar_arrive(&bars->s_free[sb]);
+      };
+      load_scores();
+      if (kKeepScores) release_scores();
+      // max of the raw scores (scale > 0 commutes with max)
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(x[i]));
-      }
+      for (int i = 0; i < 32; ++i)
+        mx4[i & 3] = fmaxf(mx4[i & 3], fmaxf(__uint_as_float(xa[i]), __uint_as_float(xb[i])));
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
       if (warp == 2) DAD_TRACE(0);
 
@@ -327,17 +340,12 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
       uint8_t* p_row = p_row0 + (j % L::kPBufs) * 2 * kPanelBytes;
       if (warp == 2) DAD_TRACE(0);
 
-      // ---- pass 2: p = exp2(s * scale * log2e - m), one FFMA + one MUFU per score; bf16 P goes
+      // ---- p = exp2(s * scale * log2e - m), one FFMA + one MUFU per score; bf16 P goes
       // to shared memory in the swizzled K-major layout. A half-row with no visible key yet has
       // m = -inf: its scores are all -inf and must give p = 0, not exp2(nan). ----
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       const float neg_m = (m == -INFINITY) ? 0.f : -m;
       auto process = [&](uint32_t (&x)[32], int ch) {
-        if (diagonal) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (ch * 32 + i > limit) x[i] = 0xff800000u;
-        }
         float pv[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -361,16 +369,12 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
           *reinterpret_cast<uint4*>(p_row + ((chunk ^ (row & 7)) << 4)) = w;
         }
       };
-      {
-        uint32_t xa[32], xb[32];
-        tmem_ld32(tS, xa);
-        tmem_ld32(tS + 32, xb);
-        tmem_wait_ld();
-        tc_fence_before_sync();
-        mbar_arrive(&bars->s_free[sb]);  // S is in registers: the next QK^T may overwrite it
-        process(xa, 0);
-        process(xb, 1);
+      if (!kKeepScores) {
+        load_scores();
+        release_scores();
       }
+      process(xa, 0);
+      process(xb, 1);
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       fence_proxy_async_smem();
       tc_fence_before_sync();
