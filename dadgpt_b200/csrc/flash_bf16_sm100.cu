@@ -194,7 +194,7 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
     // ------------------------------ MMA issuer ------------------------------
     if (elect_one()) {
       constexpr uint32_t idesc_s = make_idesc_bf16(kBM, kBN, 0, 0);  // Q, K: K-major
-      constexpr uint32_t idesc_o = make_idesc_bf16(kBM, 64, 0, 1);   // P K-major, V MN-major
+      constexpr uint32_t idesc_o = make_idesc_bf16(kBM, D, 0, 1);    // P K-major, V MN-major
       const SmemDescBase q_desc = make_desc_base_sw128(smem_u32(smem + L::kQ), 0);
       const SmemDescBase p_desc = make_desc_base_sw128(smem_u32(smem + L::kP), 0);
       const SmemDescBase k_desc0 = make_desc_base_sw128(smem_u32(smem + L::kK), 0);
@@ -211,17 +211,15 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
         DAD_TRACE(1);
         tc_fence_after_sync();
         const SmemDescBase v_desc{v_desc0.lo + s * (kStageBytes >> 4), v_desc0.hi};
+        // One MMA per 16 keys covers all D output columns: the V tile is MN-major, its 64-column
+        // panels are kPanelBytes apart, which is what the descriptor's leading byte offset says.
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
 #pragma unroll
-          for (int pn = 0; pn < kPanels; ++pn) {
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-              mma_ss(tmem + kColO + h * D + pn * 64,
-                     desc_at(p_desc, (i % L::kPBufs) * 2 * kPanelBytes + h * kPanelBytes + kk * 32),
-                     desc_at(v_desc, pn * kPanelBytes + (h * 4 + kk) * 2048), idesc_o,
-                     (i > 0 || kk > 0) ? 1u : 0u);
-            }
+          for (int kk = 0; kk < 4; ++kk) {
+            mma_ss(tmem + kColO + h * D,
+                   desc_at(p_desc, (i % L::kPBufs) * 2 * kPanelBytes + h * kPanelBytes + kk * 32),
+                   desc_at(v_desc, (h * 4 + kk) * 2048), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
           }
         }
         mma_commit(&bars->v_empty[s]);

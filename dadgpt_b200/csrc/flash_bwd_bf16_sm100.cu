@@ -169,7 +169,7 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
     // ------------------------------ MMA issuer ------------------------------
     if (elect_one()) {
       constexpr uint32_t idesc_x = make_idesc_bf16(128, 64, 0, 0);  // both operands K-major
-      constexpr uint32_t idesc_a = make_idesc_bf16(128, 64, 0, 1);  // B = streamed tile, MN-major
+      constexpr uint32_t idesc_a = make_idesc_bf16(128, D, 0, 1);   // B = streamed tile, MN-major
       const SmemDescBase r1 = make_desc_base_sw128(smem_u32(smem + L::kR1), 0);
       const SmemDescBase r2 = make_desc_base_sw128(smem_u32(smem + L::kR2), 0);
       const SmemDescBase p_desc = make_desc_base_sw128(smem_u32(smem + L::kP), 0);
@@ -214,20 +214,14 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
         if (!mbar_wait(&bars->w_full, i & 1, abort_flag)) return false;
         DAD_TRACE(1);
         tc_fence_after_sync();
+        // One MMA per 16 streamed rows covers all D output columns: the streamed tile is
+        // MN-major and its 64-column panels are kSubPanelBytes apart (the descriptor's LBO).
 #pragma unroll
-        for (int pn = 0; pn < kPanels; ++pn) {
-#pragma unroll
-          for (int kk = 0; kk < kSubRows / 16; ++kk) {
-            const uint32_t a_off = kk * 32;
-            const uint32_t b_off = pn * kSubPanelBytes + kk * 2048;
-            const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
-            if (KV) {
-              mma_ss(tmem + kColA1 + pn * 64, desc_at(p_desc, a_off), desc_at(c2, b_off), idesc_a,
-                     acc);
-            }
-            mma_ss(tmem + (KV ? kColA2 : kColA1) + pn * 64, desc_at(ds_desc, a_off),
-                   desc_at(c1, b_off), idesc_a, acc);
-          }
+        for (int kk = 0; kk < kSubRows / 16; ++kk) {
+          const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
+          if (KV) mma_ss(tmem + kColA1, desc_at(p_desc, kk * 32), desc_at(c2, kk * 2048), idesc_a, acc);
+          mma_ss(tmem + (KV ? kColA2 : kColA1), desc_at(ds_desc, kk * 32), desc_at(c1, kk * 2048),
+                 idesc_a, acc);
         }
         mma_commit(&bars->c_empty[s]);
         mma_commit(&bars->acc_done);
