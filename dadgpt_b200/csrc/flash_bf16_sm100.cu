@@ -93,10 +93,14 @@ struct FwdSmem {
   static constexpr int kK = kQ + kPanels * kPanelBytes;
   static constexpr int kV = kK + kStages * kPanels * kPanelBytes;
   static constexpr int kP = kV + kStages * kPanels * kPanelBytes;
-  // P tile buffers: two at D = 128 (one CTA per SM has the room), so the softmax of tile j
-  // never waits for P_{j-1} V_{j-1} to release the buffer; one at D = 64 (two CTAs per SM).
-  static constexpr int kPBufs = D == 128 ? 2 : 1;
-  static constexpr int kBars = kP + kPBufs * 2 * kPanelBytes;
+  // Where the probabilities P live between the softmax warps and the P V MMA. D = 128: in
+  // tensor memory, written over the scores they were computed from and read by the MMA as its
+  // A operand (an MMA with both operands in shared memory reads 8 KB per 64 clocks, all of an
+  // SM's shared-memory bandwidth, so every byte of P kept out of shared memory counts).
+  // D = 64: one bf16 tile in shared memory.
+  static constexpr bool kPTmem = D == 128;
+  static constexpr int kPBufs = 1;
+  static constexpr int kBars = kP + (kPTmem ? 0 : 2 * kPanelBytes);
   static constexpr int kBytes = kBars + 256;
 };
 
@@ -217,9 +221,12 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
         for (int h = 0; h < 2; ++h) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
-            mma_ss(tmem + kColO + h * D,
-                   desc_at(p_desc, (i % L::kPBufs) * 2 * kPanelBytes + h * kPanelBytes + kk * 32),
-                   desc_at(v_desc, (h * 4 + kk) * 2048), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+            if (L::kPTmem)  // P_i sits in the first 32 columns of each half of score buffer i % 2
+              mma_ts(tmem + kColO + h * D, tmem + kColS + (i % kSBufs) * 128 + h * 64 + kk * 8,
+                     desc_at(v_desc, (h * 4 + kk) * 2048), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+            else
+              mma_ss(tmem + kColO + h * D, desc_at(p_desc, h * kPanelBytes + kk * 32),
+                     desc_at(v_desc, (h * 4 + kk) * 2048), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
           }
         }
         mma_commit(&bars->v_empty[s]);
@@ -232,7 +239,10 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
         const int s = j % kStages;
         ok = mbar_wait(&bars->k_full[s], (j / kStages) & 1, abort_flag);
         const int sb = j % kSBufs;
-        if (ok && j >= kSBufs) ok = mbar_wait(&bars->s_free[sb], (j / kSBufs - 1) & 1, abort_flag);
+        // With P in TMEM, score buffer sb is next overwritten by S_j only after P_{j-2} V_{j-2},
+        // which was issued earlier by this same thread: the tensor pipe keeps them in order.
+        if (!L::kPTmem && ok && j >= kSBufs)
+          ok = mbar_wait(&bars->s_free[sb], (j / kSBufs - 1) & 1, abort_flag);
         if (!ok) break;
         DAD_TRACE(1);
         tc_fence_after_sync();
@@ -297,8 +307,10 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
         }
       };
       auto release_scores = [&]() {  // S is in registers: the next QK^T may overwrite it
-        tc_fence_before_sync();
-        mbar_arrive(&bars->s_free[sb]);
+        if (!L::kPTmem) {
+          tc_fence_before_sync();
+          mbar_arrive(&bars->s_free[sb]);
+        }
       };
       load_scores();
       if (kKeepScores) release_scores();
@@ -333,9 +345,9 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
         l *= corr;
         m = m_new;
       }
-      // The MMA that read this P buffer last (tile j - kPBufs) must have completed
-      if (j >= L::kPBufs && !(L::kPBufs == 1 && waited_o) && !(ok = wait_pv(j - L::kPBufs))) break;
-      uint8_t* p_row = p_row0 + (j % L::kPBufs) * 2 * kPanelBytes;
+      // P in shared memory: the MMA that read the buffer last (tile j - 1) must have completed
+      if (!L::kPTmem && j > 0 && !waited_o && !(ok = wait_pv(j - 1))) break;
+      uint8_t* p_row = p_row0;
       if (warp == 2) DAD_TRACE(0);
 
       // ---- p = exp2(s * scale * log2e - m), one FFMA + one MUFU per score; bf16 P goes
@@ -343,6 +355,7 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
       // m = -inf: its scores are all -inf and must give p = 0, not exp2(nan). ----
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       const float neg_m = (m == -INFINITY) ? 0.f : -m;
+      uint32_t pk[L::kPTmem ? 32 : 1];  // packed P of this thread when it goes to TMEM
       auto process = [&](uint32_t (&x)[32], int ch) {
         float pv[32];
 #pragma unroll
@@ -356,15 +369,21 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
           for (int i = 0; i < 32; ++i)
             pv[i] = (pv[i] != 0.f && philox_keep(rng, idx0 + i, rate)) ? pv[i] * keep_scale : 0.f;
         }
+        if (L::kPTmem) {
+          // bf16 pairs (k, k+1) per 32-bit TMEM column: 16 columns for these 32 probabilities
 #pragma unroll
-        for (int v4 = 0; v4 < 4; ++v4) {
-          uint4 w;
-          w.x = pack_bf16(pv[v4 * 8 + 0], pv[v4 * 8 + 1]);
-          w.y = pack_bf16(pv[v4 * 8 + 2], pv[v4 * 8 + 3]);
-          w.z = pack_bf16(pv[v4 * 8 + 4], pv[v4 * 8 + 5]);
-          w.w = pack_bf16(pv[v4 * 8 + 6], pv[v4 * 8 + 7]);
-          const int chunk = ch * 4 + v4;  // 16-byte chunk within the 128-byte row
-          *reinterpret_cast<uint4*>(p_row + ((chunk ^ (row & 7)) << 4)) = w;
+          for (int i = 0; i < 16; ++i) pk[ch * 16 + i] = pack_bf16(pv[2 * i], pv[2 * i + 1]);
+        } else {
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            uint4 w;
+            w.x = pack_bf16(pv[v4 * 8 + 0], pv[v4 * 8 + 1]);
+            w.y = pack_bf16(pv[v4 * 8 + 2], pv[v4 * 8 + 3]);
+            w.z = pack_bf16(pv[v4 * 8 + 4], pv[v4 * 8 + 5]);
+            w.w = pack_bf16(pv[v4 * 8 + 6], pv[v4 * 8 + 7]);
+            const int chunk = ch * 4 + v4;  // 16-byte chunk within the 128-byte row
+            *reinterpret_cast<uint4*>(p_row + ((chunk ^ (row & 7)) << 4)) = w;
+          }
         }
       };
       if (!kKeepScores) {
@@ -374,7 +393,12 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
       process(xa, 0);
       process(xb, 1);
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      fence_proxy_async_smem();
+      if (L::kPTmem) {
+        tmem_st32(tS, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
+        tmem_wait_st();
+      } else {
+        fence_proxy_async_smem();
+      }
       tc_fence_before_sync();
       mbar_arrive(&bars->p_full);
       if (warp == 2) DAD_TRACE(0);
