@@ -104,6 +104,32 @@ static __device__ long long g_trace[kTraceRoles][kTraceSlots];  // one copy per 
 #define DAD_TRACE_READER(NAME)
 #endif
 
+// Launch with programmatic stream serialization: the grid may become resident while its
+// predecessor in the stream drains, runs its set-up (barriers, TMEM, descriptor prefetch), and
+// parks in pdl_wait() until the predecessor has completed and flushed its memory. Kernels
+// launched this way call pdl_wait() before their first access to global memory.
+template <typename Kernel, typename... Args>
+cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                       Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+#endif
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 }  // namespace dadattn

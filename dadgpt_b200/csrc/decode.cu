@@ -119,8 +119,8 @@ decode_splitk_kernel(T* __restrict__ out, float* __restrict__ partial,
   static_assert(LPK >= 1 && LPK <= 32 && (LPK & (LPK - 1)) == 0, "row must split over a warp");
 
   // Everything this grid reads may have been written by the grid before it.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  pdl_wait();
+  pdl_launch_dependents();
 
   const int bh = blockIdx.x, split = blockIdx.y, splits = gridDim.y;
   const int b = bh / H;
@@ -292,23 +292,6 @@ decode_splitk_kernel(T* __restrict__ out, float* __restrict__ partial,
   }
 }
 
-// Programmatic stream serialization: the grid may be scheduled while its predecessor in the
-// stream drains; griddepcontrol.wait at the top of the kernel restores the ordering.
-template <typename Kernel, typename... Args>
-cudaError_t launch_serialized(Kernel kernel, dim3 grid, int threads, cudaStream_t st, Args... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = dim3(threads);
-  cfg.dynamicSmemBytes = 0;
-  cfg.stream = st;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr.val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kernel, args...);
-}
-
 template <int DH>
 int launch_decode_bf16(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
                        const uint16_t* v_new, uint16_t* k_cache, uint16_t* v_cache,
@@ -319,7 +302,7 @@ int launch_decode_bf16(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
   const int splits = split_count(B, H, max_len);
   unsigned* seq_tickets = tickets + static_cast<size_t>(B) * H;
   dim3 grid(static_cast<unsigned>(B) * H, splits);
-  DAD_CUDA(launch_serialized(decode_splitk_kernel<T, DH>, grid, kDecodeThreads, st,
+  DAD_CUDA(launch_pdl(decode_splitk_kernel<T, DH>, grid, dim3(kDecodeThreads), 0, st,
                              reinterpret_cast<T*>(out), partial, tickets, seq_tickets,
                              reinterpret_cast<const T*>(q), reinterpret_cast<const T*>(k_new),
                              reinterpret_cast<const T*>(v_new), reinterpret_cast<T*>(k_cache),
@@ -396,7 +379,7 @@ extern "C" int dadattn_decode_f32(float* out, const float* q, const float* k_new
   dim3 grid(H, 1);  // one CTA per head walks the whole cache: direct mode, no workspace
 #define DAD_DECODE32(DH)                                                                        \
   case DH:                                                                                      \
-    DAD_CUDA(launch_serialized(decode_splitk_kernel<float, DH>, grid, kDecodeThreads, st, out,  \
+    DAD_CUDA(launch_pdl(decode_splitk_kernel<float, DH>, grid, dim3(kDecodeThreads), 0, st, out, \
                                static_cast<float*>(nullptr), static_cast<unsigned*>(nullptr),   \
                                static_cast<unsigned*>(nullptr), q, k_new, v_new, k_cache,       \
                                v_cache, static_cast<int32_t*>(nullptr), pos, H, max_len,        \

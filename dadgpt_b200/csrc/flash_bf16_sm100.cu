@@ -169,6 +169,10 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = bars->tmem_base;
+  // Set-up is done; from here on global memory is read, which the previous grid in the stream
+  // may have produced. Once every CTA of this grid is here the next grid may start its set-up.
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -237,7 +241,9 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
 
       for (int j = 0; ok && j < n_kv; ++j) {
         const int s = j % kStages;
-        ok = mbar_wait(&bars->k_full[s], (j / kStages) & 1, abort_flag);
+        // With P in the only score buffer, P_{j-1} V_{j-1} must be issued before S_j replaces it
+        if (L::kPTmem && kSBufs == 1 && j > 0) ok = issue_pv(j - 1);
+        ok = ok && mbar_wait(&bars->k_full[s], (j / kStages) & 1, abort_flag);
         const int sb = j % kSBufs;
         // With P in TMEM, score buffer sb is next overwritten by S_j only after P_{j-2} V_{j-2},
         // which was issued earlier by this same thread: the tensor pipe keeps them in order.
@@ -256,7 +262,7 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
         mma_commit(&bars->k_empty[s]);
         mma_commit(&bars->s_full[sb]);
         DAD_TRACE(1);
-        if (j > 0) ok = issue_pv(j - 1);
+        if (!(L::kPTmem && kSBufs == 1) && j > 0) ok = issue_pv(j - 1);
       }
       if (ok) issue_pv(n_kv - 1);
     }
@@ -474,10 +480,9 @@ int launch_fwd_bf16(uint16_t* out, float* lse, const uint16_t* q, const uint16_t
   DAD_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 FwdSmem<D>::kBytes));
   dim3 grid((S + kBM - 1) / kBM, BH);
-  kern<<<grid, kFwdThreads, FwdSmem<D>::kBytes, st>>>(
-      mq, mk, mv, reinterpret_cast<__nv_bfloat16*>(out), lse, S, scale, rate,
-      make_philox(seed, offset), unit0, status);
-  DAD_LAUNCH_CHECK("flash_fwd_bf16_kernel");
+  DAD_CUDA(launch_pdl(kern, grid, dim3(kFwdThreads), FwdSmem<D>::kBytes, st, mq, mk, mv,
+                      reinterpret_cast<__nv_bfloat16*>(out), lse, S, scale, rate,
+                      make_philox(seed, offset), unit0, status));
   return DADATTN_OK;
 }
 

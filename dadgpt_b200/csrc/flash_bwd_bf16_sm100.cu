@@ -138,6 +138,10 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = bars->tmem_base;
+  // Set-up is done; from here on global memory is read, which the previous grid in the stream
+  // may have produced. Once every CTA of this grid is here the next grid may start its set-up.
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -441,20 +445,19 @@ int launch_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, float* delta, cons
   auto kq = flash_bwd_bf16_kernel<D, false, DROP>;
   DAD_CUDA(cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 BwdSmem<D, false>::kBytes));
-  kq<<<grid, kBwdThreads, BwdSmem<D, false>::kBytes, st>>>(
-      mq, mdo, mk_s, mv_s, reinterpret_cast<BF*>(dq), nullptr, lse, delta,
-      reinterpret_cast<const BF*>(out), reinterpret_cast<const BF*>(dout), S, scale, rate, rng, unit0,
-      status);
-  DAD_LAUNCH_CHECK("flash_bwd_bf16_kernel<dq>");
+  DAD_CUDA(launch_pdl(kq, grid, dim3(kBwdThreads), BwdSmem<D, false>::kBytes, st, mq, mdo, mk_s, mv_s,
+                      reinterpret_cast<BF*>(dq), static_cast<BF*>(nullptr), lse, delta,
+                      reinterpret_cast<const BF*>(out), reinterpret_cast<const BF*>(dout), S, scale,
+                      rate, rng, unit0, status));
   stage_event(1, st);
 
   auto kkv = flash_bwd_bf16_kernel<D, true, DROP>;
   DAD_CUDA(cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 BwdSmem<D, true>::kBytes));
-  kkv<<<grid, kBwdThreads, BwdSmem<D, true>::kBytes, st>>>(
-      mk, mv, mq_s, mdo_s, reinterpret_cast<BF*>(dv), reinterpret_cast<BF*>(dk), lse, delta, nullptr,
-      nullptr, S, scale, rate, rng, unit0, status);
-  DAD_LAUNCH_CHECK("flash_bwd_bf16_kernel<dkdv>");
+  DAD_CUDA(launch_pdl(kkv, grid, dim3(kBwdThreads), BwdSmem<D, true>::kBytes, st, mk, mv, mq_s, mdo_s,
+                      reinterpret_cast<BF*>(dv), reinterpret_cast<BF*>(dk), lse, delta,
+                      static_cast<const BF*>(nullptr), static_cast<const BF*>(nullptr), S, scale,
+                      rate, rng, unit0, status));
   stage_event(2, st);
   return DADATTN_OK;
 }
