@@ -34,8 +34,8 @@ METRIC = "causal_attn_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
-# capture summarised under profiles/ (None until a capture exists for the current kernel).
-NCU_TRAFFIC_BYTES = {"flash_bwd_bf16_kernel<dkdv>": None}
+# capture summarised in profiles/flash_bf16_fwd_bwd_gpt2_T1024_D64.md.
+NCU_TRAFFIC_BYTES = {"flash_bwd_bf16_kernel<dkdv>": 122.0e6}
 
 
 def load_peaks():
@@ -347,8 +347,8 @@ def run_ours(args):
             q, k, v = qs[s % len(qs)]
             dad.gpu_flash_attention_forward_bf16(o_, l_, q, k, v, BH, T, D, scale)
         ms = timed(f_, K, Wm)
-        shorter[f"T{T}"] = {"ms": ms, "tflops": W.attn_flops(BH, T, D)[0] / ms / 1e9,
-                            "hbm_gbs": W.attn_bytes(BH, T, D)[0] / ms / 1e6, "bound": "hbm"}
+        shorter[f"T{T}"] = {"ms": ms, "tflops": W.attn_flops(BH, T, D)[0] * world / ms / 1e9,
+                            "hbm_gbs": W.attn_bytes(BH, T, D)[0] * world / ms / 1e6, "bound": "hbm"}
         del qs
 
     decode = bench_decode(dad, W, dev, world, barrier, max_over_ranks, torch)
