@@ -24,6 +24,7 @@ SIGNATURES = {
     "dadattn_flash_fwd_bf16": (I, [P, P, P, P, P, I, I, I, F, F, U64, U64, I64, P]),
     "dadattn_flash_bwd_bf16_workspace_bytes": (SZ, [I, I, I]),
     "dadattn_flash_bwd_bf16": (I, [P, P, P, P, SZ, P, P, P, P, P, P, I, I, I, F, F, U64, U64, I64, P]),
+    "dadattn_set_bwd_deterministic": (I, [I]),
     "dadattn_set_stage_events": (I, [P, I]),
     "dadattn_decode_f32": (I, [P] * 6 + [I, I, I, I, F, P]),
     "dadattn_decode_workspace_bytes": (SZ, [I, I, I, I]),

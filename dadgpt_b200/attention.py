@@ -95,6 +95,13 @@ def gpu_flash_attention_backward_bf16(dq, dk, dv, workspace, dout, out, lse, q, 
         _ptr(q), _ptr(k), _ptr(v), BH, S, d_head, scale, rate, seed, offset, unit0, _stream()))
 
 
+def set_backward_deterministic(on: bool) -> None:
+    """Head size 64: choose between the single-pass backward (default; dQ summed across key tiles
+    in arrival order, so its last bits may vary between runs) and the two-kernel backward that,
+    like the reference, accumulates nothing across thread blocks."""
+    _lib.check(_lib.load().dadattn_set_bwd_deterministic(1 if on else 0))
+
+
 def dropout_mask(mask: torch.Tensor, rate: float, seed: int, offset: int = 0, first: int = 0):
     """Fill ``mask`` (uint8, flat) with the reference's keep(1)/drop(0) mask
     (reference cuda/gpu_ops.cu:712-734) for elements first .. first+numel-1."""

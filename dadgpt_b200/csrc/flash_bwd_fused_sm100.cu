@@ -1,0 +1,477 @@
+// bf16 fused causal attention backward for sm_100a, head size 64: dQ, dK and dV in ONE pass.
+//
+// The reference computes the probabilities twice, once in its dK/dV kernel and once in its dQ
+// kernel (cuda/attention.cu:88-205): 7 GEMM-sized products for 5 gradients' worth. Here a CTA
+// owns 128 keys of one (batch, head), streams the 128-query tiles that can see them, and per
+// tile forms S = Q K^T and dP = dO V^T once, then
+//     dV += P^T dO        dK += dS^T Q        dQ_tile = dS K
+// with p = exp2(S scale log2e - lse log2e), ds = p (dP - delta) scale as in the reference.
+// dK/dV accumulate in tensor memory over the whole loop; each tile's dQ contribution is added
+// into an fp32 workspace with a TMA reduce-add (several CTAs, one per key tile, contribute to
+// the same queries), and a last pass rounds the workspace to bf16. The sums into the workspace
+// happen in whatever order the CTAs reach them, so dQ may differ in its last bits from run to
+// run; dadattn_set_bwd_deterministic(1) selects the two-kernel path of
+// flash_bwd_bf16_sm100.cu, which has no such sums.
+//
+// Rows of the score tile are queries (one TMEM lane each), so lse and delta are per-thread
+// scalars. P and dS are written once, bf16, row-major [query][key] in the 128-byte swizzled
+// layout: dS is the K-major A operand of dQ = dS K, and the same bytes read as an MN-major A
+// operand are dS^T (resp. P^T) for dK (resp. dV). The Q / dO tiles are K-major A operands of the
+// score GEMMs and MN-major B operands of dK / dV; K is the K-major B operand of S and the
+// MN-major B operand of dQ.
+//   warp 0       TMA producer           warp 1       MMA issuer + TMEM owner
+//   warps 2-17   compute: four warps per TMEM lane quadrant, 32 of the 128 key columns each
+#include <cuda_bf16.h>
+
+#include <cfloat>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace dadattn {
+namespace {
+
+using namespace ptx;
+
+constexpr int kFT = 128;                  // tile edge: queries per step, keys per CTA
+constexpr int kFD = 64;                   // head size
+constexpr int kFPanel = 128 * 128;        // [128 rows][64 bf16] swizzled panel
+constexpr int kFThreads = 18 * 32;
+constexpr int kFCompute = 16 * 32;
+constexpr int kFStages = 2;
+constexpr float kFLog2e = 1.4426950408889634f;
+
+struct FusedSmem {
+  static constexpr int kK = 0;
+  static constexpr int kV = kK + kFPanel;
+  static constexpr int kQ = kV + kFPanel;
+  static constexpr int kDO = kQ + kFStages * kFPanel;
+  static constexpr int kP = kDO + kFStages * kFPanel;   // [128 q][128 keys] bf16, two panels
+  static constexpr int kDS = kP + 2 * kFPanel;
+  static constexpr int kDQ = kDS + 2 * kFPanel;         // [128 q][64] fp32, two 128-byte panels
+  static constexpr int kBars = kDQ + 2 * kFPanel;
+  static constexpr int kBytes = kBars + 256;
+};
+
+struct FusedBars {
+  uint64_t kv_full, q_full[kFStages], do_full[kFStages], qdo_empty[kFStages];
+  uint64_t x_full, x_free, w_full, acc_done, dq_drained, dq_staged, dq_sent;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// TMA reduce-add of one [128 rows][32 fp32] panel from shared memory into the dQ workspace.
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, const void* smem_src, int x,
+                                                  int y, int z) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+template <bool DROP>
+__global__ void __launch_bounds__(kFThreads, 1)
+flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                       const __grid_constant__ CUtensorMap map_dqw, __nv_bfloat16* __restrict__ dk,
+                       __nv_bfloat16* __restrict__ dv, const float* __restrict__ lse,
+                       const float* __restrict__ delta, int S, float scale, float rate, PhiloxKey rng,
+                       int64_t unit0, int* __restrict__ status) {
+  using L = FusedSmem;
+  constexpr int D = kFD;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 320, kColDQ = 384;
+
+  extern __shared__ __align__(1024) uint8_t smem[];
+  FusedBars* bars = reinterpret_cast<FusedBars*>(smem + L::kBars);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int n_tiles = (S + kFT - 1) / kFT;
+  const int bh = blockIdx.y;
+  const int kt = blockIdx.x;            // low key tiles see the most queries and come first
+  const int n_it = n_tiles - kt;        // query tiles kt .. n_tiles-1
+  const int k0 = kt * kFT;
+
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicExch(status, DADATTN_E_CUDA);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->kv_full, 1);
+    for (int s = 0; s < kFStages; ++s) {
+      mbar_init(&bars->q_full[s], 1);
+      mbar_init(&bars->do_full[s], 1);
+      mbar_init(&bars->qdo_empty[s], 1);
+    }
+    mbar_init(&bars->x_full, 1);
+    mbar_init(&bars->x_free, kFCompute);
+    mbar_init(&bars->w_full, kFCompute);
+    mbar_init(&bars->acc_done, 1);
+    mbar_init(&bars->dq_drained, kFCompute);
+    mbar_init(&bars->dq_staged, kFCompute);
+    mbar_init(&bars->dq_sent, 1);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = bars->tmem_base;
+  pdl_wait();
+  pdl_launch_dependents();
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (elect_one()) {
+      prefetch_tensormap(&map_q);
+      prefetch_tensormap(&map_k);
+      prefetch_tensormap(&map_v);
+      prefetch_tensormap(&map_do);
+      prefetch_tensormap(&map_dqw);
+      mbar_arrive_expect_tx(&bars->kv_full, 2 * kFPanel);
+      tma_load_3d(smem + L::kK, &map_k, &bars->kv_full, 0, k0, bh);
+      tma_load_3d(smem + L::kV, &map_v, &bars->kv_full, 0, k0, bh);
+      for (int i = 0; i < n_it; ++i) {
+        const int s = i % kFStages, use = i / kFStages;
+        if (use > 0 && !mbar_wait(&bars->qdo_empty[s], (use - 1) & 1, abort_flag)) break;
+        const int q0 = (kt + i) * kFT;
+        mbar_arrive_expect_tx(&bars->q_full[s], kFPanel);
+        tma_load_3d(smem + L::kQ + s * kFPanel, &map_q, &bars->q_full[s], 0, q0, bh);
+        mbar_arrive_expect_tx(&bars->do_full[s], kFPanel);
+        tma_load_3d(smem + L::kDO + s * kFPanel, &map_do, &bars->do_full[s], 0, q0, bh);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (elect_one()) {
+      constexpr uint32_t idesc_x = make_idesc_bf16(128, 128, 0, 0);   // S, dP: both K-major
+      constexpr uint32_t idesc_t = make_idesc_bf16(128, 64, 1, 1);    // dV, dK: A and B MN-major
+      constexpr uint32_t idesc_q = make_idesc_bf16(128, 64, 0, 1);    // dQ: A K-major, B MN-major
+      const SmemDescBase k_kmaj = make_desc_base_sw128(smem_u32(smem + L::kK), 0);
+      const SmemDescBase v_kmaj = make_desc_base_sw128(smem_u32(smem + L::kV), 0);
+      const SmemDescBase q0_desc = make_desc_base_sw128(smem_u32(smem + L::kQ), 0);
+      const SmemDescBase do0_desc = make_desc_base_sw128(smem_u32(smem + L::kDO), 0);
+      // P / dS read as MN-major A: the two 64-key panels are kFPanel apart (leading byte offset)
+      const SmemDescBase p_t = make_desc_base_sw128(smem_u32(smem + L::kP), kFPanel);
+      const SmemDescBase ds_t = make_desc_base_sw128(smem_u32(smem + L::kDS), kFPanel);
+      const SmemDescBase ds_k = make_desc_base_sw128(smem_u32(smem + L::kDS), 0);
+      bool ok = mbar_wait(&bars->kv_full, 0, abort_flag);
+
+      auto issue_x = [&](int i) -> bool {
+        const int s = i % kFStages;
+        const uint32_t par = (i / kFStages) & 1;
+        const SmemDescBase qd{q0_desc.lo + s * (kFPanel >> 4), q0_desc.hi};
+        const SmemDescBase dd{do0_desc.lo + s * (kFPanel >> 4), do0_desc.hi};
+        if (!mbar_wait(&bars->q_full[s], par, abort_flag)) return false;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_ss(tmem + kColS, desc_at(qd, kk * 32), desc_at(k_kmaj, kk * 32), idesc_x, kk > 0 ? 1u : 0u);
+        if (!mbar_wait(&bars->do_full[s], par, abort_flag)) return false;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_ss(tmem + kColDP, desc_at(dd, kk * 32), desc_at(v_kmaj, kk * 32), idesc_x, kk > 0 ? 1u : 0u);
+        mma_commit(&bars->x_full);
+        return true;
+      };
+      auto issue_acc = [&](int i) -> bool {
+        const int s = i % kFStages;
+        const SmemDescBase qd{q0_desc.lo + s * (kFPanel >> 4), q0_desc.hi};
+        const SmemDescBase dd{do0_desc.lo + s * (kFPanel >> 4), do0_desc.hi};
+        if (!mbar_wait(&bars->w_full, i & 1, abort_flag)) return false;
+        // the previous tile's dQ must have left tensor memory before this one overwrites it
+        if (i > 0 && !mbar_wait(&bars->dq_drained, (i - 1) & 1, abort_flag)) return false;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < kFT / 16; ++kk) {   // K dimension = 128 queries, 16 per MMA
+          const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
+          // A = P^T / dS^T: 16 query rows (2048 bytes) further down per step; B = dO / Q rows
+          mma_ss(tmem + kColDV, desc_at(p_t, kk * 2048), desc_at(dd, kk * 2048), idesc_t, acc);
+          mma_ss(tmem + kColDK, desc_at(ds_t, kk * 2048), desc_at(qd, kk * 2048), idesc_t, acc);
+        }
+#pragma unroll
+        for (int kk = 0; kk < kFT / 16; ++kk) {   // K dimension = 128 keys
+          mma_ss(tmem + kColDQ, desc_at(ds_k, (kk / 4) * kFPanel + (kk % 4) * 32),
+                 desc_at(k_kmaj, kk * 2048), idesc_q, kk > 0 ? 1u : 0u);
+        }
+        mma_commit(&bars->qdo_empty[s]);
+        mma_commit(&bars->acc_done);
+        return true;
+      };
+
+      ok = ok && issue_x(0);
+      for (int i = 0; ok && i < n_it; ++i) {
+        if (i + 1 < n_it) ok = mbar_wait(&bars->x_free, i & 1, abort_flag) && issue_x(i + 1);
+        ok = ok && issue_acc(i);
+      }
+    }
+  } else {
+    // ------------------------------ compute warps ------------------------------
+    const int cw = warp - 2;              // 0..15
+    const int quad = warp % 4;            // TMEM lane quadrant of this warp
+    const int cg = cw / 4;                // which 32 key columns of the 128 (and 16 dQ columns)
+    const int ct = cw * 32 + lane;
+    const int row = quad * 32 + lane;     // query row within the tile = TMEM lane
+    const uint32_t tlane = tmem + (static_cast<uint32_t>(quad * 32) << 16);
+    const float scale_log2 = scale * kFLog2e;
+    const float keep_scale = DROP ? 1.0f / (1.0f - rate) : 1.0f;
+    const size_t vec_base = static_cast<size_t>(bh) * S;
+    uint8_t* p_row = smem + L::kP + (cg / 2) * kFPanel + row * 128;
+    uint8_t* ds_row = smem + L::kDS + (cg / 2) * kFPanel + row * 128;
+    uint8_t* dq_row = smem + L::kDQ + (cg / 2) * kFPanel + row * 128;
+    bool ok = true;
+
+    // dQ of tile i: TMEM -> swizzled fp32 staging -> TMA reduce-add into the workspace
+    auto drain_dq = [&](int i) -> bool {
+      if (!mbar_wait(&bars->acc_done, i & 1, abort_flag)) return false;
+      tc_fence_after_sync();
+      uint32_t o[16];
+      tmem_ld16(tlane + kColDQ + cg * 16, o);
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      mbar_arrive(&bars->dq_drained);
+      // the reduce of the previous tile must have finished reading the staging buffer
+      if (i > 0 && !mbar_wait(&bars->dq_sent, (i - 1) & 1, abort_flag)) return false;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int chunk = (cg & 1) * 4 + c;
+        *reinterpret_cast<uint4*>(dq_row + ((chunk ^ (row & 7)) << 4)) =
+            make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(&bars->dq_staged);
+      if (ct == 0) {
+        if (!mbar_wait(&bars->dq_staged, i & 1, abort_flag)) return false;
+        const int q0 = (kt + i) * kFT;
+        tma_reduce_add_3d(&map_dqw, smem + L::kDQ, 0, q0, bh);
+        tma_reduce_add_3d(&map_dqw, smem + L::kDQ + kFPanel, 32, q0, bh);
+        bulk_commit();
+        bulk_wait_read0();
+        mbar_arrive(&bars->dq_sent);
+      }
+      return true;
+    };
+
+    for (int i = 0; i < n_it; ++i) {
+      const int q0 = (kt + i) * kFT;
+      const int q = q0 + row;
+      const bool diagonal = (i == 0);
+      // per-row scalars; queries beyond S contribute nothing (p = exp2(-inf) = 0)
+      const float row_lse2 = q < S ? lse[vec_base + q] * kFLog2e : INFINITY;
+      const float row_delta = q < S ? delta[vec_base + q] : 0.f;
+      if (!(ok = mbar_wait(&bars->x_full, i & 1, abort_flag))) break;
+      tc_fence_after_sync();
+      uint32_t x1[32], x2[32];
+      tmem_ld32(tlane + kColS + cg * 32, x1);
+      tmem_ld32(tlane + kColDP + cg * 32, x2);
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      mbar_arrive(&bars->x_free);  // scores are in registers: the next tile's GEMMs may overwrite
+
+      if (i > 0 && !(ok = drain_dq(i - 1))) break;  // implies P / dS of tile i-1 were consumed
+
+      uint32_t pw[16], dw[16];
+#pragma unroll
+      for (int c = 0; c < 32; c += 2) {
+        float pv[2], dv2[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int key = k0 + cg * 32 + c + e;
+          float p = ex2(fmaf(__uint_as_float(x1[c + e]), scale_log2, -row_lse2));
+          if (diagonal && key > q) p = 0.f;
+          float g = __uint_as_float(x2[c + e]);
+          float pd = p;
+          if (DROP) {
+            const uint64_t idx = (static_cast<uint64_t>(unit0 + bh) * S + q) * S + key;
+            const float mk = (p != 0.f && philox_keep(rng, idx, rate)) ? keep_scale : 0.f;
+            pd = p * mk;
+            g *= mk;
+          }
+          pv[e] = pd;
+          dv2[e] = p * (g - row_delta) * scale;
+        }
+        pw[c / 2] = pack_bf16(pv[0], pv[1]);
+        dw[c / 2] = pack_bf16(dv2[0], dv2[1]);
+      }
+#pragma unroll
+      for (int v4 = 0; v4 < 4; ++v4) {
+        const int chunk = (cg & 1) * 4 + v4;  // 16-byte chunk within the 128-byte row of the panel
+        const int off = (chunk ^ (row & 7)) << 4;
+        *reinterpret_cast<uint4*>(p_row + off) =
+            make_uint4(pw[4 * v4], pw[4 * v4 + 1], pw[4 * v4 + 2], pw[4 * v4 + 3]);
+        *reinterpret_cast<uint4*>(ds_row + off) =
+            make_uint4(dw[4 * v4], dw[4 * v4 + 1], dw[4 * v4 + 2], dw[4 * v4 + 3]);
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(&bars->w_full);
+    }
+
+    // last tile's dQ, then dK / dV
+    if (ok) ok = drain_dq(n_it - 1);
+    if (ok && ct == 0) bulk_wait0();
+    if (ok) {
+      // cg 0,1 store dV columns [32 cg', +32), cg 2,3 store dK columns likewise
+      const int key = k0 + row;
+      const uint32_t col = (cg < 2 ? kColDV : kColDK) + (cg & 1) * 32;
+      __nv_bfloat16* dst = (cg < 2 ? dv : dk) + (vec_base + key) * D + (cg & 1) * 32;
+      uint32_t o[32];
+      tmem_ld32(tlane + col, o);
+      tmem_wait_ld();
+      if (key < S) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          *reinterpret_cast<uint4*>(dst + i * 8) = make_uint4(
+              pack_bf16(__uint_as_float(o[8 * i + 0]), __uint_as_float(o[8 * i + 1])),
+              pack_bf16(__uint_as_float(o[8 * i + 2]), __uint_as_float(o[8 * i + 3])),
+              pack_bf16(__uint_as_float(o[8 * i + 4]), __uint_as_float(o[8 * i + 5])),
+              pack_bf16(__uint_as_float(o[8 * i + 6]), __uint_as_float(o[8 * i + 7])));
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+  if (threadIdx.x == 0 && bars->abort_flag) atomicExch(status, DADATTN_E_TIMEOUT);
+}
+
+// delta[r] = sum_d dO[r,d] O[r,d] (reference flash_delta_kernel, cuda/attention.cu:76-85) and the
+// zero fill of the fp32 dQ workspace, in one pass over the rows.
+__global__ void fused_prepare_kernel(float* __restrict__ delta, float* __restrict__ dq_ws,
+                                     const __nv_bfloat16* __restrict__ dout,
+                                     const __nv_bfloat16* __restrict__ out, int64_t rows) {
+  constexpr int D = kFD, Lr = D / 8;  // 8 lanes per row
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t r = t / Lr;
+  const int c = static_cast<int>(t % Lr) * 8;
+  float sum = 0.f;
+  if (r < rows) {
+    const uint4 a = *reinterpret_cast<const uint4*>(dout + r * D + c);
+    const uint4 b = *reinterpret_cast<const uint4*>(out + r * D + c);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      sum = fmaf(__uint_as_float(aw[i] << 16), __uint_as_float(bw[i] << 16), sum);
+      sum = fmaf(__uint_as_float(aw[i] & 0xffff0000u), __uint_as_float(bw[i] & 0xffff0000u), sum);
+    }
+    float4* z = reinterpret_cast<float4*>(dq_ws + r * D + c);
+    z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll
+  for (int o = Lr / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (r < rows && c == 0) delta[r] = sum;
+}
+
+// dQ workspace (fp32) -> dq (bf16)
+__global__ void fused_convert_kernel(__nv_bfloat16* __restrict__ dq, const float* __restrict__ dq_ws,
+                                     int64_t n8) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= n8) return;
+  const float4 a = *reinterpret_cast<const float4*>(dq_ws + t * 8);
+  const float4 b = *reinterpret_cast<const float4*>(dq_ws + t * 8 + 4);
+  *reinterpret_cast<uint4*>(dq + t * 8) = make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w),
+                                                     pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// 3-D map over the fp32 workspace [BH, S, 64] with a 32 x 128 x 1 box and 128-byte swizzle
+int make_dq_workspace_map(CUtensorMap* map, float* ws, int BH, int S) {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  if (!fn) return fail(DADATTN_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[3] = {kFD, static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(BH)};
+  const cuuint64_t strides[2] = {kFD * 4, static_cast<cuuint64_t>(S) * kFD * 4};
+  const cuuint32_t box[3] = {32, kFT, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, ws, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(DADATTN_E_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return DADATTN_OK;
+}
+
+}  // namespace
+
+// Workspace: delta [BH,S] fp32, then the dQ accumulator [BH,S,64] fp32 (256-byte aligned).
+size_t fused_bwd_workspace_bytes(int BH, int S) {
+  const size_t delta_bytes = (static_cast<size_t>(BH) * S * sizeof(float) + 255) / 256 * 256;
+  return delta_bytes + static_cast<size_t>(BH) * S * kFD * sizeof(float);
+}
+
+int launch_bwd_fused_d64(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspace, const uint16_t* dout,
+                         const uint16_t* out, const float* lse, const uint16_t* q, const uint16_t* k,
+                         const uint16_t* v, int BH, int S, float scale, float rate, uint64_t seed,
+                         uint64_t offset, int64_t unit0, cudaStream_t st) {
+  using BF = __nv_bfloat16;
+  float* delta = static_cast<float*>(workspace);
+  float* dq_ws = reinterpret_cast<float*>(static_cast<char*>(workspace) +
+                                          (static_cast<size_t>(BH) * S * sizeof(float) + 255) / 256 * 256);
+  CUtensorMap mq, mk, mv, mdo, mws;
+  if (int rc = make_tensor_map_bf16(&mq, q, BH, S, kFD, kFT)) return rc;
+  if (int rc = make_tensor_map_bf16(&mk, k, BH, S, kFD, kFT)) return rc;
+  if (int rc = make_tensor_map_bf16(&mv, v, BH, S, kFD, kFT)) return rc;
+  if (int rc = make_tensor_map_bf16(&mdo, dout, BH, S, kFD, kFT)) return rc;
+  if (int rc = make_dq_workspace_map(&mws, dq_ws, BH, S)) return rc;
+  int* status = device_status_word();
+  if (!status) return DADATTN_E_CUDA;
+
+  const int64_t rows = static_cast<int64_t>(BH) * S;
+  const int64_t prep_threads = rows * (kFD / 8);
+  DAD_CUDA(launch_pdl(fused_prepare_kernel, dim3(static_cast<unsigned>((prep_threads + 255) / 256)),
+                      dim3(256), 0, st, delta, dq_ws, reinterpret_cast<const BF*>(dout),
+                      reinterpret_cast<const BF*>(out), rows));
+  const PhiloxKey rng = make_philox(seed, offset);
+  dim3 grid((S + kFT - 1) / kFT, BH);
+  const bool drop = rate > 0.f;
+  auto kern = drop ? flash_bwd_fused_kernel<true> : flash_bwd_fused_kernel<false>;
+  DAD_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FusedSmem::kBytes));
+  DAD_CUDA(launch_pdl(kern, grid, dim3(kFThreads), FusedSmem::kBytes, st, mq, mk, mv, mdo, mws,
+                      reinterpret_cast<BF*>(dk), reinterpret_cast<BF*>(dv), lse,
+                      static_cast<const float*>(delta), S, scale, rate, rng, unit0, status));
+  const int64_t n8 = rows * kFD / 8;
+  DAD_CUDA(launch_pdl(fused_convert_kernel, dim3(static_cast<unsigned>((n8 + 255) / 256)), dim3(256), 0,
+                      st, reinterpret_cast<BF*>(dq), static_cast<const float*>(dq_ws), n8));
+  return DADATTN_OK;
+}
+
+}  // namespace dadattn

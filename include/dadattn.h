@@ -97,8 +97,9 @@ int dadattn_flash_fwd_bf16(uint16_t* out, float* lse, const uint16_t* q, const u
 
 /* bf16 form of gpu_flash_attention_backward (reference cuda/attention.cu:241-252). dq,dk,dv bf16,
  * written not accumulated. workspace: caller-owned scratch of at least
- * dadattn_flash_bwd_bf16_workspace_bytes(BH,S,D) bytes, 16-byte aligned (it takes the place of
- * the fp32 call's `delta` scratch; contents are overwritten). */
+ * dadattn_flash_bwd_bf16_workspace_bytes(BH,S,D) bytes, 256-byte aligned (it takes the place of
+ * the fp32 call's `delta` scratch and, at head size 64, also holds an fp32 dQ accumulator;
+ * contents are overwritten). */
 size_t dadattn_flash_bwd_bf16_workspace_bytes(int BH, int S, int D);
 int dadattn_flash_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspace,
                            size_t workspace_bytes, const uint16_t* dout, const uint16_t* out,
@@ -107,10 +108,19 @@ int dadattn_flash_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* works
                            uint64_t seed, uint64_t offset, int64_t unit0,
                            dadattn_stream_t stream);
 
+/* At head size 64 the backward is a single-pass kernel that adds each key tile's dQ contribution
+ * into an fp32 accumulator in the workspace (TMA reduce-add): about twice as fast, but the order
+ * of those additions is not fixed, so dQ may differ in its last bits between runs (dK and dV do
+ * not). dadattn_set_bwd_deterministic(1) makes the calling thread use the two-kernel backward,
+ * which like the reference (cuda/attention.cu:4-6) accumulates nothing across thread blocks;
+ * 0 (the default) restores the single-pass kernel. No counterpart in the reference. */
+int dadattn_set_bwd_deterministic(int on);
+
 /* Measurement aid (no counterpart in the reference): when `events` (an array of `count`
  * cudaEvent_t) is set for the calling thread, dadattn_flash_bwd_bf16 records events[0] before
- * its dQ kernel (which also forms delta), [1] before the dK/dV kernel and [2] after it, on the
- * call's stream. Pass NULL to switch it off. */
+ * its first kernel and [2] after its last, on the call's stream; in the two-kernel (deterministic
+ * or head size 128) backward [1] separates the dQ kernel from the dK/dV kernel. Pass NULL to
+ * switch it off. */
 int dadattn_set_stage_events(void** events, int count);
 
 /* ---- KV-cache decode --------------------------------------------------------------------- */

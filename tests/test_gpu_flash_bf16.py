@@ -10,7 +10,8 @@ import torch
 
 import dadgpt_b200 as dad
 from dadgpt_b200 import workloads as W
-from dadgpt_b200.attention import device_status, flash_backward_bf16_workspace_bytes
+from dadgpt_b200.attention import (device_status, flash_backward_bf16_workspace_bytes,
+                                   set_backward_deterministic)
 from tests.gpu_util import dev_bf16, max_abs, rel_l2
 
 pytestmark = pytest.mark.gpu
@@ -109,9 +110,17 @@ def bwd(dout, out, lse, tensors, scale, dev, **kw):
     return [t.float().cpu().numpy() for t in (dq, dk, dv)], fdo
 
 
+@pytest.fixture(params=[False, True], ids=["single_pass", "deterministic"])
+def bwd_mode(request):
+    """Both backward paths of head size 64 (head size 128 has only the two-kernel one)."""
+    set_backward_deterministic(request.param)
+    yield request.param
+    set_backward_deterministic(False)
+
+
 @pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("S", [1, 31, 128, 129, 200, 384, 700])
-def test_backward_shapes_against_oracle(cuda, oracle, S, D):
+def test_backward_shapes_against_oracle(cuda, oracle, bwd_mode, S, D):
     rng = np.random.default_rng(31 * D + S)
     BH = 3
     q, k, v, dout = (rng.standard_normal((BH, S, D), dtype=np.float32) for _ in range(4))
@@ -124,7 +133,7 @@ def test_backward_shapes_against_oracle(cuda, oracle, S, D):
 
 
 @pytest.mark.parametrize("D", [64, 128])
-def test_backward_dropout_against_oracle(cuda, oracle, D):
+def test_backward_dropout_against_oracle(cuda, oracle, bwd_mode, D):
     rng = np.random.default_rng(41)
     BH, S = 3, 200
     q, k, v, dout = (rng.standard_normal((BH, S, D), dtype=np.float32) for _ in range(4))
@@ -137,14 +146,17 @@ def test_backward_dropout_against_oracle(cuda, oracle, D):
     # a shard of the (batch x head) axis reproduces its slice of the whole
     part, _ = bwd(dout[1:], out[1:].contiguous(), lse[1:].contiguous(), [t[1:].contiguous() for t in ts],
                   scale, cuda, unit0=1, **kw)
-    for a, b in zip(part, grads):
-        assert np.array_equal(a, b[1:])
+    for a, b, name in zip(part, grads, ("dq", "dk", "dv")):
+        if name == "dq" and D == 64 and not bwd_mode:  # summed in arrival order: last bits may differ
+            assert rel_l2(a, b[1:]) <= 1e-2
+        else:
+            assert np.array_equal(a, b[1:])
 
 
-def test_backward_gpt2_shape_subset_and_properties(cuda, oracle):
+def test_backward_gpt2_shape_subset_and_properties(cuda, oracle, bwd_mode):
     """Full GPT-2-124M shape with dropout 0.1 (Philox seed 42, offset 0): three (b,h) units against
     the oracle (each with its own global unit index, which fixes its mask); all units: finite and
-    bit-identical across two calls (no atomics anywhere in the backward)."""
+    bit-identical across two calls (dQ of the single-pass kernel: equal up to summation order)."""
     shape = W.gpt2(1024)
     q, k, v = W.qkv(shape)
     dout = W.dout(shape)
@@ -160,8 +172,11 @@ def test_backward_gpt2_shape_subset_and_properties(cuda, oracle):
     for g in grads:
         assert np.isfinite(g).all()
     grads2, _ = bwd(dout, out, lse, ts, shape.scale, cuda, **kw)
-    for a, b in zip(grads, grads2):
-        assert np.array_equal(a, b)
+    for a, b, name in zip(grads, grads2, ("dq", "dk", "dv")):
+        if name == "dq" and not bwd_mode:  # the single-pass kernel sums dQ in arrival order
+            assert rel_l2(a, b) <= 1e-2
+        else:
+            assert np.array_equal(a, b), name
 
 
 def test_backward_matches_fp32_kernel_on_same_inputs(cuda):
