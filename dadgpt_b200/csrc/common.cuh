@@ -130,6 +130,14 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 }
 #endif
 
+// Optional timing hooks of the bf16 backward (dadattn_set_stage_events): event i is recorded on
+// the call's stream before its i-th kernel, and one more after the last kernel.
+extern thread_local cudaEvent_t* g_stage_events;
+extern thread_local int g_stage_event_count;
+inline void stage_event(int i, cudaStream_t st) {
+  if (g_stage_events && i < g_stage_event_count) cudaEventRecord(g_stage_events[i], st);
+}
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 }  // namespace dadattn

@@ -411,13 +411,6 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
   if (threadIdx.x == 0 && bars->abort_flag) atomicExch(status, DADATTN_E_TIMEOUT);
 }
 
-thread_local cudaEvent_t* g_stage_events = nullptr;
-thread_local int g_stage_event_count = 0;
-
-inline void stage_event(int i, cudaStream_t st) {
-  if (g_stage_events && i < g_stage_event_count) cudaEventRecord(g_stage_events[i], st);
-}
-
 template <int D, bool DROP>
 int launch_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, float* delta, const uint16_t* dout,
                     const uint16_t* out, const float* lse, const uint16_t* q, const uint16_t* k,
@@ -470,6 +463,9 @@ int launch_bwd_fused_d64(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspa
                          const uint16_t* out, const float* lse, const uint16_t* q, const uint16_t* k,
                          const uint16_t* v, int BH, int S, float scale, float rate, uint64_t seed,
                          uint64_t offset, int64_t unit0, cudaStream_t st);
+
+thread_local cudaEvent_t* g_stage_events = nullptr;
+thread_local int g_stage_event_count = 0;
 
 namespace {
 thread_local int g_deterministic = 0;

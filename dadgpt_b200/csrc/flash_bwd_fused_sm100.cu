@@ -21,6 +21,7 @@
 // MN-major B operand of dQ.
 //   warp 0       TMA producer           warp 1       MMA issuer + TMEM owner
 //   warps 2-17   compute: four warps per TMEM lane quadrant, 32 of the 128 key columns each
+//   warp 18      dQ reducer: issues the TMA reduce-adds and recycles the two staging buffers
 #include <cuda_bf16.h>
 
 #include <cfloat>
@@ -36,9 +37,10 @@ using namespace ptx;
 constexpr int kFT = 128;                  // tile edge: queries per step, keys per CTA
 constexpr int kFD = 64;                   // head size
 constexpr int kFPanel = 128 * 128;        // [128 rows][64 bf16] swizzled panel
-constexpr int kFThreads = 18 * 32;
+constexpr int kFThreads = 19 * 32;
 constexpr int kFCompute = 16 * 32;
 constexpr int kFStages = 2;
+constexpr int kFDqBufs = 2;               // fp32 dQ staging buffers in shared memory
 constexpr float kFLog2e = 1.4426950408889634f;
 
 struct FusedSmem {
@@ -49,13 +51,13 @@ struct FusedSmem {
   static constexpr int kP = kDO + kFStages * kFPanel;   // [128 q][128 keys] bf16, two panels
   static constexpr int kDS = kP + 2 * kFPanel;
   static constexpr int kDQ = kDS + 2 * kFPanel;         // [128 q][64] fp32, two 128-byte panels
-  static constexpr int kBars = kDQ + 2 * kFPanel;
+  static constexpr int kBars = kDQ + kFDqBufs * 2 * kFPanel;
   static constexpr int kBytes = kBars + 256;
 };
 
 struct FusedBars {
   uint64_t kv_full, q_full[kFStages], do_full[kFStages], qdo_empty[kFStages];
-  uint64_t x_full, x_free, w_full, acc_done, dq_drained, dq_staged, dq_sent;
+  uint64_t x_full, x_free, w_full, acc_done, dq_drained, dq_staged[kFDqBufs], dq_sent[kFDqBufs];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -71,6 +73,9 @@ __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, const 
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read0() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_read1() {
+  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
 }
 __device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
@@ -125,8 +130,10 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     mbar_init(&bars->w_full, kFCompute);
     mbar_init(&bars->acc_done, 1);
     mbar_init(&bars->dq_drained, kFCompute);
-    mbar_init(&bars->dq_staged, kFCompute);
-    mbar_init(&bars->dq_sent, 1);
+    for (int b = 0; b < kFDqBufs; ++b) {
+      mbar_init(&bars->dq_staged[b], kFCompute);
+      mbar_init(&bars->dq_sent[b], 1);
+    }
     bars->abort_flag = 0;
     fence_mbar_init();
   }
@@ -177,6 +184,7 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const SmemDescBase ds_t = make_desc_base_sw128(smem_u32(smem + L::kDS), kFPanel);
       const SmemDescBase ds_k = make_desc_base_sw128(smem_u32(smem + L::kDS), 0);
       bool ok = mbar_wait(&bars->kv_full, 0, abort_flag);
+      DAD_TRACE_DECL;
 
       auto issue_x = [&](int i) -> bool {
         const int s = i % kFStages;
@@ -193,6 +201,7 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int kk = 0; kk < D / 16; ++kk)
           mma_ss(tmem + kColDP, desc_at(dd, kk * 32), desc_at(v_kmaj, kk * 32), idesc_x, kk > 0 ? 1u : 0u);
         mma_commit(&bars->x_full);
+        DAD_TRACE(1);
         return true;
       };
       auto issue_acc = [&](int i) -> bool {
@@ -200,8 +209,7 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const SmemDescBase qd{q0_desc.lo + s * (kFPanel >> 4), q0_desc.hi};
         const SmemDescBase dd{do0_desc.lo + s * (kFPanel >> 4), do0_desc.hi};
         if (!mbar_wait(&bars->w_full, i & 1, abort_flag)) return false;
-        // the previous tile's dQ must have left tensor memory before this one overwrites it
-        if (i > 0 && !mbar_wait(&bars->dq_drained, (i - 1) & 1, abort_flag)) return false;
+        DAD_TRACE(1);
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < kFT / 16; ++kk) {   // K dimension = 128 queries, 16 per MMA
@@ -210,6 +218,10 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           mma_ss(tmem + kColDV, desc_at(p_t, kk * 2048), desc_at(dd, kk * 2048), idesc_t, acc);
           mma_ss(tmem + kColDK, desc_at(ds_t, kk * 2048), desc_at(qd, kk * 2048), idesc_t, acc);
         }
+        // the previous tile's dQ must have left tensor memory before this one overwrites it; the
+        // compute warps read it right after they publish P / dS, while dV / dK are running
+        if (i > 0 && !mbar_wait(&bars->dq_drained, (i - 1) & 1, abort_flag)) return false;
+        tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < kFT / 16; ++kk) {   // K dimension = 128 keys
           mma_ss(tmem + kColDQ, desc_at(ds_k, (kk / 4) * kFPanel + (kk % 4) * 32),
@@ -217,6 +229,7 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         mma_commit(&bars->qdo_empty[s]);
         mma_commit(&bars->acc_done);
+        DAD_TRACE(1);
         return true;
       };
 
@@ -225,6 +238,27 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (i + 1 < n_it) ok = mbar_wait(&bars->x_free, i & 1, abort_flag) && issue_x(i + 1);
         ok = ok && issue_acc(i);
       }
+    }
+  } else if (warp == 18) {
+    // ------------------------------ dQ reducer ------------------------------
+    // Tile i's reduce-add reads staging buffer i % 2; the buffer is handed back once the reduce
+    // of tile i+1 has been queued behind it and the TMA unit has finished reading tile i's.
+    if (elect_one()) {
+      bool ok = true;
+      for (int i = 0; i < n_it; ++i) {
+        const int b = i % kFDqBufs;
+        if (!(ok = mbar_wait(&bars->dq_staged[b], (i / kFDqBufs) & 1, abort_flag))) break;
+        const uint8_t* src = smem + L::kDQ + b * 2 * kFPanel;
+        const int q0 = (kt + i) * kFT;
+        tma_reduce_add_3d(&map_dqw, src, 0, q0, bh);
+        tma_reduce_add_3d(&map_dqw, src + kFPanel, 32, q0, bh);
+        bulk_commit();
+        if (i > 0) {
+          bulk_wait_read1();
+          mbar_arrive(&bars->dq_sent[(i - 1) % kFDqBufs]);
+        }
+      }
+      bulk_wait0();   // every sum has landed before the CTA retires
     }
   } else {
     // ------------------------------ compute warps ------------------------------
@@ -239,20 +273,22 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const size_t vec_base = static_cast<size_t>(bh) * S;
     uint8_t* p_row = smem + L::kP + (cg / 2) * kFPanel + row * 128;
     uint8_t* ds_row = smem + L::kDS + (cg / 2) * kFPanel + row * 128;
-    uint8_t* dq_row = smem + L::kDQ + (cg / 2) * kFPanel + row * 128;
+    uint8_t* dq_row0 = smem + L::kDQ + (cg / 2) * kFPanel + row * 128;
     bool ok = true;
+    DAD_TRACE_DECL;
 
-    // dQ of tile i: TMEM -> swizzled fp32 staging -> TMA reduce-add into the workspace
+    // dQ of tile i: TMEM -> swizzled fp32 staging buffer i % 2, which the reducer warp sends on.
+    // The caller has seen acc_done of tile i.
     auto drain_dq = [&](int i) -> bool {
-      if (!mbar_wait(&bars->acc_done, i & 1, abort_flag)) return false;
-      tc_fence_after_sync();
+      const int b = i % kFDqBufs;
       uint32_t o[16];
       tmem_ld16(tlane + kColDQ + cg * 16, o);
       tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive(&bars->dq_drained);
-      // the reduce of the previous tile must have finished reading the staging buffer
-      if (i > 0 && !mbar_wait(&bars->dq_sent, (i - 1) & 1, abort_flag)) return false;
+      // the reduce that used this buffer two tiles ago must have finished reading it
+      if (i >= kFDqBufs && !mbar_wait(&bars->dq_sent[b], (i / kFDqBufs - 1) & 1, abort_flag)) return false;
+      uint8_t* dq_row = dq_row0 + b * 2 * kFPanel;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int chunk = (cg & 1) * 4 + c;
@@ -260,27 +296,32 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
       }
       fence_proxy_async_smem();
-      mbar_arrive(&bars->dq_staged);
-      if (ct == 0) {
-        if (!mbar_wait(&bars->dq_staged, i & 1, abort_flag)) return false;
-        const int q0 = (kt + i) * kFT;
-        tma_reduce_add_3d(&map_dqw, smem + L::kDQ, 0, q0, bh);
-        tma_reduce_add_3d(&map_dqw, smem + L::kDQ + kFPanel, 32, q0, bh);
-        bulk_commit();
-        bulk_wait_read0();
-        mbar_arrive(&bars->dq_sent);
-      }
+      mbar_arrive(&bars->dq_staged[b]);
       return true;
     };
+
+    // per-row scalars, fetched one tile ahead: their loads share the SM's path to L2 with the dQ
+    // reduce traffic and would otherwise stall the arithmetic. Queries beyond S contribute
+    // nothing (p = exp2(-inf) = 0).
+    auto load_row = [&](int i, float& l2, float& dl) {
+      const int qq = (kt + i) * kFT + row;
+      const bool in = i < n_it && qq < S;
+      l2 = in ? lse[vec_base + qq] * kFLog2e : INFINITY;
+      dl = in ? delta[vec_base + qq] : 0.f;
+    };
+    float next_lse2, next_delta;
+    load_row(0, next_lse2, next_delta);
 
     for (int i = 0; i < n_it; ++i) {
       const int q0 = (kt + i) * kFT;
       const int q = q0 + row;
       const bool diagonal = (i == 0);
-      // per-row scalars; queries beyond S contribute nothing (p = exp2(-inf) = 0)
-      const float row_lse2 = q < S ? lse[vec_base + q] * kFLog2e : INFINITY;
-      const float row_delta = q < S ? delta[vec_base + q] : 0.f;
+      const float row_lse2 = next_lse2, row_delta = next_delta;
+      load_row(i + 1, next_lse2, next_delta);
+      if (warp == 2) DAD_TRACE(0);
+      if (warp == 17) DAD_TRACE(2);
       if (!(ok = mbar_wait(&bars->x_full, i & 1, abort_flag))) break;
+      if (warp == 2) DAD_TRACE(0);
       tc_fence_after_sync();
       uint32_t x1[32], x2[32];
       tmem_ld32(tlane + kColS + cg * 32, x1);
@@ -288,9 +329,9 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive(&bars->x_free);  // scores are in registers: the next tile's GEMMs may overwrite
+      if (warp == 2) DAD_TRACE(0);
 
-      if (i > 0 && !(ok = drain_dq(i - 1))) break;  // implies P / dS of tile i-1 were consumed
-
+      // The arithmetic runs out of registers while the tensor core is still busy with tile i-1.
       uint32_t pw[16], dw[16];
 #pragma unroll
       for (int c = 0; c < 32; c += 2) {
@@ -314,6 +355,13 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         pw[c / 2] = pack_bf16(pv[0], pv[1]);
         dw[c / 2] = pack_bf16(dv2[0], dv2[1]);
       }
+      if (warp == 2) DAD_TRACE(0);
+      // P / dS of tile i-1 consumed and its dQ complete in tensor memory
+      if (i > 0) {
+        if (!(ok = mbar_wait(&bars->acc_done, (i - 1) & 1, abort_flag))) break;
+        tc_fence_after_sync();
+      }
+      if (warp == 2) DAD_TRACE(0);
 #pragma unroll
       for (int v4 = 0; v4 < 4; ++v4) {
         const int chunk = (cg & 1) * 4 + v4;  // 16-byte chunk within the 128-byte row of the panel
@@ -325,11 +373,15 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       fence_proxy_async_smem();
       mbar_arrive(&bars->w_full);
+      if (warp == 2) DAD_TRACE(0);
+      if (warp == 17) DAD_TRACE(2);
+      if (i > 0 && !(ok = drain_dq(i - 1))) break;
     }
 
     // last tile's dQ, then dK / dV
+    if (ok) ok = mbar_wait(&bars->acc_done, (n_it - 1) & 1, abort_flag);
+    tc_fence_after_sync();
     if (ok) ok = drain_dq(n_it - 1);
-    if (ok && ct == 0) bulk_wait0();
     if (ok) {
       // cg 0,1 store dV columns [32 cg', +32), cg 2,3 store dK columns likewise
       const int key = k0 + row;
@@ -431,6 +483,9 @@ int make_dq_workspace_map(CUtensorMap* map, float* ws, int BH, int S) {
 }
 
 }  // namespace
+}  // namespace dadattn
+DAD_TRACE_READER(dadattn_trace_read_fused)
+namespace dadattn {
 
 // Workspace: delta [BH,S] fp32, then the dQ accumulator [BH,S,64] fp32 (256-byte aligned).
 size_t fused_bwd_workspace_bytes(int BH, int S) {
@@ -457,9 +512,11 @@ int launch_bwd_fused_d64(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspa
 
   const int64_t rows = static_cast<int64_t>(BH) * S;
   const int64_t prep_threads = rows * (kFD / 8);
+  stage_event(0, st);
   DAD_CUDA(launch_pdl(fused_prepare_kernel, dim3(static_cast<unsigned>((prep_threads + 255) / 256)),
                       dim3(256), 0, st, delta, dq_ws, reinterpret_cast<const BF*>(dout),
                       reinterpret_cast<const BF*>(out), rows));
+  stage_event(1, st);
   const PhiloxKey rng = make_philox(seed, offset);
   dim3 grid((S + kFT - 1) / kFT, BH);
   const bool drop = rate > 0.f;
@@ -468,9 +525,11 @@ int launch_bwd_fused_d64(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspa
   DAD_CUDA(launch_pdl(kern, grid, dim3(kFThreads), FusedSmem::kBytes, st, mq, mk, mv, mdo, mws,
                       reinterpret_cast<BF*>(dk), reinterpret_cast<BF*>(dv), lse,
                       static_cast<const float*>(delta), S, scale, rate, rng, unit0, status));
+  stage_event(2, st);
   const int64_t n8 = rows * kFD / 8;
   DAD_CUDA(launch_pdl(fused_convert_kernel, dim3(static_cast<unsigned>((n8 + 255) / 256)), dim3(256), 0,
                       st, reinterpret_cast<BF*>(dq), static_cast<const float*>(dq_ws), n8));
+  stage_event(3, st);
   return DADATTN_OK;
 }
 

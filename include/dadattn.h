@@ -117,10 +117,11 @@ int dadattn_flash_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* works
 int dadattn_set_bwd_deterministic(int on);
 
 /* Measurement aid (no counterpart in the reference): when `events` (an array of `count`
- * cudaEvent_t) is set for the calling thread, dadattn_flash_bwd_bf16 records events[0] before
- * its first kernel and [2] after its last, on the call's stream; in the two-kernel (deterministic
- * or head size 128) backward [1] separates the dQ kernel from the dK/dV kernel. Pass NULL to
- * switch it off. */
+ * cudaEvent_t) is set for the calling thread, dadattn_flash_bwd_bf16 records events[i] on the
+ * call's stream before its i-th kernel and one more event after its last kernel. The single-pass
+ * backward (head size 64) launches three kernels (delta + workspace clear, the fused gradient
+ * kernel, fp32 -> bf16 of dQ: four events); the two-kernel backward launches dQ, then dK/dV
+ * (three events). Events beyond `count` are not recorded. Pass NULL to switch it off. */
 int dadattn_set_stage_events(void** events, int count);
 
 /* ---- KV-cache decode --------------------------------------------------------------------- */
