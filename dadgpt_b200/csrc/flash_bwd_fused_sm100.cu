@@ -40,24 +40,26 @@ constexpr int kFPanel = 128 * 128;        // [128 rows][64 bf16] swizzled panel
 constexpr int kFThreads = 19 * 32;
 constexpr int kFCompute = 16 * 32;
 constexpr int kFStages = 2;
-constexpr int kFDqBufs = 2;               // fp32 dQ staging buffers in shared memory
+constexpr int kFRing = 4;                 // entries of the work-item ring (a power of two)
 constexpr float kFLog2e = 1.4426950408889634f;
 
 struct FusedSmem {
-  static constexpr int kK = 0;
-  static constexpr int kV = kK + kFPanel;
-  static constexpr int kQ = kV + kFPanel;
+  static constexpr int kK = 0;                          // two buffers: items alternate
+  static constexpr int kV = kK + 2 * kFPanel;
+  static constexpr int kQ = kV + 2 * kFPanel;
   static constexpr int kDO = kQ + kFStages * kFPanel;
   static constexpr int kP = kDO + kFStages * kFPanel;   // [128 q][128 keys] bf16, two panels
   static constexpr int kDS = kP + 2 * kFPanel;
   static constexpr int kDQ = kDS + 2 * kFPanel;         // [128 q][64] fp32, two 128-byte panels
-  static constexpr int kBars = kDQ + kFDqBufs * 2 * kFPanel;
+  static constexpr int kBars = kDQ + 2 * kFPanel;
   static constexpr int kBytes = kBars + 256;
 };
 
 struct FusedBars {
-  uint64_t kv_full, q_full[kFStages], do_full[kFStages], qdo_empty[kFStages];
-  uint64_t x_full, x_free, w_full, acc_done, dq_drained, dq_staged[kFDqBufs], dq_sent[kFDqBufs];
+  uint64_t kv_full[2], dkv_sent[2], q_full[kFStages], do_full[kFStages], qdo_empty[kFStages];
+  uint64_t item_ready[kFRing], item_free[kFRing];
+  uint64_t x_full, x_free, w_full, acc_done, dq_drained, dq_staged, dq_sent, dkv_staged;
+  int ring[kFRing];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -67,6 +69,15 @@ __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, const 
                                                   int y, int z) {
   asm volatile(
       "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+// TMA store of one [128 rows][64 bf16] swizzled panel from shared memory; rows beyond the
+// tensor's extent are dropped.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* smem_src, int x, int y,
+                                             int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
       ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
@@ -90,14 +101,52 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "memory");
 }
 
+// One item of work = (key tile kt, batch x head bh): the CTA that takes it streams the n_it query
+// tiles that can see those keys. Items are numbered so that batch x head units come in groups of
+// `group_bh` (their Q, dO and dQ rows stay in L2 while the group is worked on) and, inside a
+// group, key tile by key tile: the key tiles with the most queries first.
+struct Item {
+  int kt, bh, n_it;
+};
+__device__ __forceinline__ Item decode_item(int item, int BH, int n_tiles, int group_bh) {
+  const int per_group = group_bh * n_tiles;
+  const int grp = item / per_group;
+  const int r = item - grp * per_group;
+  const int bh0 = grp * group_bh;
+  const int gb = min(group_bh, BH - bh0);
+  Item t;
+  t.kt = r / gb;
+  t.bh = bh0 + r - t.kt * gb;
+  t.n_it = n_tiles - t.kt;
+  return t;
+}
+
+// Items are handed out by a global counter; the producer thread takes them and publishes each
+// through a four-entry ring in shared memory, which the other roles read in the same order.
+struct ItemFeed {
+  FusedBars* bars;
+  volatile int* abort_flag;
+  int n_read;
+  // the next item of this CTA, or n_items when there is none (or the kernel is aborting)
+  __device__ __forceinline__ int fetch(int n_items) {
+    const int slot = n_read & (kFRing - 1);
+    if (!mbar_wait(&bars->item_ready[slot], (n_read / kFRing) & 1, abort_flag)) return n_items;
+    const int v = *reinterpret_cast<volatile int*>(&bars->ring[slot]);
+    mbar_arrive(&bars->item_free[slot]);
+    ++n_read;
+    return v;
+  }
+};
+
 template <bool DROP>
 __global__ void __launch_bounds__(kFThreads, 1)
 flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                       const __grid_constant__ CUtensorMap map_dqw, __nv_bfloat16* __restrict__ dk,
-                       __nv_bfloat16* __restrict__ dv, const float* __restrict__ lse,
-                       const float* __restrict__ delta, int S, float scale, float rate, PhiloxKey rng,
-                       int64_t unit0, int* __restrict__ status) {
+                       const __grid_constant__ CUtensorMap map_dqw, const __grid_constant__ CUtensorMap map_dk,
+                       const __grid_constant__ CUtensorMap map_dv, const float* __restrict__ lse,
+                       const float* __restrict__ delta, int* __restrict__ item_counter, int BH, int S,
+                       int group_bh, float scale, float rate, PhiloxKey rng, int64_t unit0,
+                       int* __restrict__ status) {
   using L = FusedSmem;
   constexpr int D = kFD;
   constexpr uint32_t kTmemCols = 512;
@@ -109,31 +158,34 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int n_tiles = (S + kFT - 1) / kFT;
-  const int bh = blockIdx.y;
-  const int kt = blockIdx.x;            // low key tiles see the most queries and come first
-  const int n_it = n_tiles - kt;        // query tiles kt .. n_tiles-1
-  const int k0 = kt * kFT;
+  const int n_items = n_tiles * BH;
 
   if ((smem_u32(smem) & 1023u) != 0) {
     if (threadIdx.x == 0) atomicExch(status, DADATTN_E_CUDA);
     return;
   }
   if (threadIdx.x == 0) {
-    mbar_init(&bars->kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->kv_full[s], 1);
+      mbar_init(&bars->dkv_sent[s], 1);
+    }
     for (int s = 0; s < kFStages; ++s) {
       mbar_init(&bars->q_full[s], 1);
       mbar_init(&bars->do_full[s], 1);
       mbar_init(&bars->qdo_empty[s], 1);
+    }
+    for (int s = 0; s < kFRing; ++s) {
+      mbar_init(&bars->item_ready[s], 1);
+      mbar_init(&bars->item_free[s], kFCompute + 2);   // compute threads, MMA issuer, reducer
     }
     mbar_init(&bars->x_full, 1);
     mbar_init(&bars->x_free, kFCompute);
     mbar_init(&bars->w_full, kFCompute);
     mbar_init(&bars->acc_done, 1);
     mbar_init(&bars->dq_drained, kFCompute);
-    for (int b = 0; b < kFDqBufs; ++b) {
-      mbar_init(&bars->dq_staged[b], kFCompute);
-      mbar_init(&bars->dq_sent[b], 1);
-    }
+    mbar_init(&bars->dq_staged, kFCompute);
+    mbar_init(&bars->dq_sent, 1);
+    mbar_init(&bars->dkv_staged, kFCompute);
     bars->abort_flag = 0;
     fence_mbar_init();
   }
@@ -149,24 +201,51 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   pdl_launch_dependents();
 
   if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
+    // ------------------------------ scheduler + TMA producer ------------------------------
     if (elect_one()) {
       prefetch_tensormap(&map_q);
       prefetch_tensormap(&map_k);
       prefetch_tensormap(&map_v);
       prefetch_tensormap(&map_do);
-      prefetch_tensormap(&map_dqw);
-      mbar_arrive_expect_tx(&bars->kv_full, 2 * kFPanel);
-      tma_load_3d(smem + L::kK, &map_k, &bars->kv_full, 0, k0, bh);
-      tma_load_3d(smem + L::kV, &map_v, &bars->kv_full, 0, k0, bh);
-      for (int i = 0; i < n_it; ++i) {
-        const int s = i % kFStages, use = i / kFStages;
-        if (use > 0 && !mbar_wait(&bars->qdo_empty[s], (use - 1) & 1, abort_flag)) break;
-        const int q0 = (kt + i) * kFT;
-        mbar_arrive_expect_tx(&bars->q_full[s], kFPanel);
-        tma_load_3d(smem + L::kQ + s * kFPanel, &map_q, &bars->q_full[s], 0, q0, bh);
-        mbar_arrive_expect_tx(&bars->do_full[s], kFPanel);
-        tma_load_3d(smem + L::kDO + s * kFPanel, &map_do, &bars->do_full[s], 0, q0, bh);
+      int n_pub = 0;
+      auto publish = [&](int item) -> bool {
+        const int slot = n_pub & (kFRing - 1);
+        if (n_pub >= kFRing &&
+            !mbar_wait(&bars->item_free[slot], (n_pub / kFRing - 1) & 1, abort_flag))
+          return false;
+        *reinterpret_cast<volatile int*>(&bars->ring[slot]) = item;
+        mbar_arrive(&bars->item_ready[slot]);
+        ++n_pub;
+        return true;
+      };
+      // the first item is the CTA's own index; the counter hands out the rest
+      int cur = static_cast<int>(blockIdx.x);
+      int nxt = static_cast<int>(gridDim.x) + atomicAdd(item_counter, 1);
+      bool ok = publish(cur);
+      int g = 0;
+      for (int j = 0; ok && cur < n_items; ++j) {
+        // publish the following item (or the end mark) now: the other roles look one item ahead
+        ok = publish(nxt);
+        const int after = nxt < n_items ? static_cast<int>(gridDim.x) + atomicAdd(item_counter, 1) : nxt;
+        const Item t = decode_item(cur, BH, n_tiles, group_bh);
+        // K / V go to the buffer of the item before last, once its dK / dV have left that buffer
+        const int kb = j & 1;
+        if (ok && j >= 2) ok = mbar_wait(&bars->dkv_sent[kb], ((j >> 1) - 1) & 1, abort_flag);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&bars->kv_full[kb], 2 * kFPanel);
+        tma_load_3d(smem + L::kK + kb * kFPanel, &map_k, &bars->kv_full[kb], 0, t.kt * kFT, t.bh);
+        tma_load_3d(smem + L::kV + kb * kFPanel, &map_v, &bars->kv_full[kb], 0, t.kt * kFT, t.bh);
+        for (int i = 0; i < t.n_it; ++i, ++g) {
+          const int s = g % kFStages, use = g / kFStages;
+          if (use > 0 && !(ok = mbar_wait(&bars->qdo_empty[s], (use - 1) & 1, abort_flag))) break;
+          const int q0 = (t.kt + i) * kFT;
+          mbar_arrive_expect_tx(&bars->q_full[s], kFPanel);
+          tma_load_3d(smem + L::kQ + s * kFPanel, &map_q, &bars->q_full[s], 0, q0, t.bh);
+          mbar_arrive_expect_tx(&bars->do_full[s], kFPanel);
+          tma_load_3d(smem + L::kDO + s * kFPanel, &map_do, &bars->do_full[s], 0, q0, t.bh);
+        }
+        cur = nxt;
+        nxt = after;
       }
     }
   } else if (warp == 1) {
@@ -175,57 +254,63 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       constexpr uint32_t idesc_x = make_idesc_bf16(128, 128, 0, 0);   // S, dP: both K-major
       constexpr uint32_t idesc_t = make_idesc_bf16(128, 64, 1, 1);    // dV, dK: A and B MN-major
       constexpr uint32_t idesc_q = make_idesc_bf16(128, 64, 0, 1);    // dQ: A K-major, B MN-major
-      const SmemDescBase k_kmaj = make_desc_base_sw128(smem_u32(smem + L::kK), 0);
-      const SmemDescBase v_kmaj = make_desc_base_sw128(smem_u32(smem + L::kV), 0);
+      const SmemDescBase k0_desc = make_desc_base_sw128(smem_u32(smem + L::kK), 0);
+      const SmemDescBase v0_desc = make_desc_base_sw128(smem_u32(smem + L::kV), 0);
       const SmemDescBase q0_desc = make_desc_base_sw128(smem_u32(smem + L::kQ), 0);
       const SmemDescBase do0_desc = make_desc_base_sw128(smem_u32(smem + L::kDO), 0);
       // P / dS read as MN-major A: the two 64-key panels are kFPanel apart (leading byte offset)
       const SmemDescBase p_t = make_desc_base_sw128(smem_u32(smem + L::kP), kFPanel);
       const SmemDescBase ds_t = make_desc_base_sw128(smem_u32(smem + L::kDS), kFPanel);
       const SmemDescBase ds_k = make_desc_base_sw128(smem_u32(smem + L::kDS), 0);
-      bool ok = mbar_wait(&bars->kv_full, 0, abort_flag);
       DAD_TRACE_DECL;
 
-      auto issue_x = [&](int i) -> bool {
-        const int s = i % kFStages;
-        const uint32_t par = (i / kFStages) & 1;
+      // S = Q K^T and dP = dO V^T of tile g (counted over all items of this CTA), K / V buffer kb
+      auto issue_x = [&](int g, int kb) -> bool {
+        const int s = g % kFStages;
+        const uint32_t par = (g / kFStages) & 1;
         const SmemDescBase qd{q0_desc.lo + s * (kFPanel >> 4), q0_desc.hi};
         const SmemDescBase dd{do0_desc.lo + s * (kFPanel >> 4), do0_desc.hi};
+        const SmemDescBase kd{k0_desc.lo + kb * (kFPanel >> 4), k0_desc.hi};
+        const SmemDescBase vd{v0_desc.lo + kb * (kFPanel >> 4), v0_desc.hi};
         if (!mbar_wait(&bars->q_full[s], par, abort_flag)) return false;
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          mma_ss(tmem + kColS, desc_at(qd, kk * 32), desc_at(k_kmaj, kk * 32), idesc_x, kk > 0 ? 1u : 0u);
+          mma_ss(tmem + kColS, desc_at(qd, kk * 32), desc_at(kd, kk * 32), idesc_x, kk > 0 ? 1u : 0u);
         if (!mbar_wait(&bars->do_full[s], par, abort_flag)) return false;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          mma_ss(tmem + kColDP, desc_at(dd, kk * 32), desc_at(v_kmaj, kk * 32), idesc_x, kk > 0 ? 1u : 0u);
+          mma_ss(tmem + kColDP, desc_at(dd, kk * 32), desc_at(vd, kk * 32), idesc_x, kk > 0 ? 1u : 0u);
         mma_commit(&bars->x_full);
         DAD_TRACE(1);
         return true;
       };
-      auto issue_acc = [&](int i) -> bool {
-        const int s = i % kFStages;
+      // dV += P^T dO, dK += dS^T Q (fresh accumulators on an item's first tile), dQ_tile = dS K
+      auto issue_acc = [&](int g, int kb, bool first_of_item) -> bool {
+        const int s = g % kFStages;
         const SmemDescBase qd{q0_desc.lo + s * (kFPanel >> 4), q0_desc.hi};
         const SmemDescBase dd{do0_desc.lo + s * (kFPanel >> 4), do0_desc.hi};
-        if (!mbar_wait(&bars->w_full, i & 1, abort_flag)) return false;
+        const SmemDescBase kd{k0_desc.lo + kb * (kFPanel >> 4), k0_desc.hi};
+        // w_full also says that the compute warps have taken the previous item's dK / dV out of
+        // tensor memory
+        if (!mbar_wait(&bars->w_full, g & 1, abort_flag)) return false;
         DAD_TRACE(1);
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < kFT / 16; ++kk) {   // K dimension = 128 queries, 16 per MMA
-          const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
+          const uint32_t acc = (!first_of_item || kk > 0) ? 1u : 0u;
           // A = P^T / dS^T: 16 query rows (2048 bytes) further down per step; B = dO / Q rows
           mma_ss(tmem + kColDV, desc_at(p_t, kk * 2048), desc_at(dd, kk * 2048), idesc_t, acc);
           mma_ss(tmem + kColDK, desc_at(ds_t, kk * 2048), desc_at(qd, kk * 2048), idesc_t, acc);
         }
         // the previous tile's dQ must have left tensor memory before this one overwrites it; the
         // compute warps read it right after they publish P / dS, while dV / dK are running
-        if (i > 0 && !mbar_wait(&bars->dq_drained, (i - 1) & 1, abort_flag)) return false;
+        if (g > 0 && !mbar_wait(&bars->dq_drained, (g - 1) & 1, abort_flag)) return false;
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < kFT / 16; ++kk) {   // K dimension = 128 keys
           mma_ss(tmem + kColDQ, desc_at(ds_k, (kk / 4) * kFPanel + (kk % 4) * 32),
-                 desc_at(k_kmaj, kk * 2048), idesc_q, kk > 0 ? 1u : 0u);
+                 desc_at(kd, kk * 2048), idesc_q, kk > 0 ? 1u : 0u);
         }
         mma_commit(&bars->qdo_empty[s]);
         mma_commit(&bars->acc_done);
@@ -233,171 +318,240 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         return true;
       };
 
-      ok = ok && issue_x(0);
-      for (int i = 0; ok && i < n_it; ++i) {
-        if (i + 1 < n_it) ok = mbar_wait(&bars->x_free, i & 1, abort_flag) && issue_x(i + 1);
-        ok = ok && issue_acc(i);
+      ItemFeed feed{bars, abort_flag, 0};
+      int cur = feed.fetch(n_items);
+      int nxt = cur < n_items ? feed.fetch(n_items) : n_items;
+      bool ok = cur < n_items && mbar_wait(&bars->kv_full[0], 0, abort_flag) && issue_x(0, 0);
+      int g = 0;
+      for (int j = 0; ok && cur < n_items; ++j) {
+        const int n_it = decode_item(cur, BH, n_tiles, group_bh).n_it;
+        for (int i = 0; ok && i < n_it; ++i, ++g) {
+          // The next tile's score GEMMs go first, so the arithmetic on them overlaps this tile's
+          // accumulating GEMMs; across an item boundary they use the other K / V buffer.
+          if (i + 1 < n_it) {
+            ok = mbar_wait(&bars->x_free, g & 1, abort_flag) && issue_x(g + 1, j & 1);
+          } else if (nxt < n_items) {
+            const int kbn = (j + 1) & 1;
+            ok = mbar_wait(&bars->x_free, g & 1, abort_flag) &&
+                 mbar_wait(&bars->kv_full[kbn], ((j + 1) >> 1) & 1, abort_flag) && issue_x(g + 1, kbn);
+          }
+          ok = ok && issue_acc(g, j & 1, i == 0);
+        }
+        cur = nxt;
+        nxt = cur < n_items ? feed.fetch(n_items) : n_items;
       }
     }
   } else if (warp == 18) {
-    // ------------------------------ dQ reducer ------------------------------
-    // Tile i's reduce-add reads staging buffer i % 2; the buffer is handed back once the reduce
-    // of tile i+1 has been queued behind it and the TMA unit has finished reading tile i's.
+    // ------------------------------ dQ reducer / dK, dV writer ------------------------------
     if (elect_one()) {
+      prefetch_tensormap(&map_dqw);
+      prefetch_tensormap(&map_dk);
+      prefetch_tensormap(&map_dv);
+      ItemFeed feed{bars, abort_flag, 0};
+      int cur = feed.fetch(n_items);
+      int nxt = cur < n_items ? feed.fetch(n_items) : n_items;
+      int g = 0;
       bool ok = true;
-      for (int i = 0; i < n_it; ++i) {
-        const int b = i % kFDqBufs;
-        if (!(ok = mbar_wait(&bars->dq_staged[b], (i / kFDqBufs) & 1, abort_flag))) break;
-        const uint8_t* src = smem + L::kDQ + b * 2 * kFPanel;
-        const int q0 = (kt + i) * kFT;
-        tma_reduce_add_3d(&map_dqw, src, 0, q0, bh);
-        tma_reduce_add_3d(&map_dqw, src + kFPanel, 32, q0, bh);
-        bulk_commit();
-        if (i > 0) {
-          bulk_wait_read1();
-          mbar_arrive(&bars->dq_sent[(i - 1) % kFDqBufs]);
+      for (int j = 0; ok && cur < n_items; ++j) {
+        const Item t = decode_item(cur, BH, n_tiles, group_bh);
+        for (int i = 0; ok && i < t.n_it; ++i, ++g) {
+          if (!(ok = mbar_wait(&bars->dq_staged, g & 1, abort_flag))) break;
+          const int q0 = (t.kt + i) * kFT;
+          tma_reduce_add_3d(&map_dqw, smem + L::kDQ, 0, q0, t.bh);
+          tma_reduce_add_3d(&map_dqw, smem + L::kDQ + kFPanel, 32, q0, t.bh);
+          bulk_commit();
+          if (i + 1 < t.n_it) {
+            bulk_wait_read0();
+            mbar_arrive(&bars->dq_sent);
+          } else {
+            // The item's dK / dV were staged (in its K / V buffers) before the dQ of its last
+            // tile. Their stores go behind the reduce, so that the dQ staging buffer is handed
+            // back as soon as the reduce has read it; the K / V buffers follow.
+            if (!(ok = mbar_wait(&bars->dkv_staged, j & 1, abort_flag))) break;
+            tma_store_3d(&map_dk, smem + L::kK + (j & 1) * kFPanel, 0, t.kt * kFT, t.bh);
+            tma_store_3d(&map_dv, smem + L::kV + (j & 1) * kFPanel, 0, t.kt * kFT, t.bh);
+            bulk_commit();
+            bulk_wait_read1();
+            mbar_arrive(&bars->dq_sent);
+            bulk_wait_read0();
+            mbar_arrive(&bars->dkv_sent[j & 1]);
+          }
         }
+        cur = nxt;
+        nxt = cur < n_items ? feed.fetch(n_items) : n_items;
       }
-      bulk_wait0();   // every sum has landed before the CTA retires
+      bulk_wait0();   // every sum and store has landed before the CTA retires
     }
   } else {
     // ------------------------------ compute warps ------------------------------
     const int cw = warp - 2;              // 0..15
     const int quad = warp % 4;            // TMEM lane quadrant of this warp
     const int cg = cw / 4;                // which 32 key columns of the 128 (and 16 dQ columns)
-    const int ct = cw * 32 + lane;
     const int row = quad * 32 + lane;     // query row within the tile = TMEM lane
     const uint32_t tlane = tmem + (static_cast<uint32_t>(quad * 32) << 16);
     const float scale_log2 = scale * kFLog2e;
     const float keep_scale = DROP ? 1.0f / (1.0f - rate) : 1.0f;
-    const size_t vec_base = static_cast<size_t>(bh) * S;
     uint8_t* p_row = smem + L::kP + (cg / 2) * kFPanel + row * 128;
     uint8_t* ds_row = smem + L::kDS + (cg / 2) * kFPanel + row * 128;
-    uint8_t* dq_row0 = smem + L::kDQ + (cg / 2) * kFPanel + row * 128;
+    uint8_t* dq_row = smem + L::kDQ + (cg / 2) * kFPanel + row * 128;
     bool ok = true;
     DAD_TRACE_DECL;
 
-    // dQ of tile i: TMEM -> swizzled fp32 staging buffer i % 2, which the reducer warp sends on.
-    // The caller has seen acc_done of tile i.
-    auto drain_dq = [&](int i) -> bool {
-      const int b = i % kFDqBufs;
+    // dQ of tile t: TMEM -> swizzled fp32 staging, which the reducer warp sends on. The caller
+    // has seen acc_done of tile t.
+    auto drain_dq = [&](int t) -> bool {
       uint32_t o[16];
       tmem_ld16(tlane + kColDQ + cg * 16, o);
       tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive(&bars->dq_drained);
-      // the reduce that used this buffer two tiles ago must have finished reading it
-      if (i >= kFDqBufs && !mbar_wait(&bars->dq_sent[b], (i / kFDqBufs - 1) & 1, abort_flag)) return false;
-      uint8_t* dq_row = dq_row0 + b * 2 * kFPanel;
+      // the reduce of the previous tile must have finished reading the staging buffer
+      if (t > 0 && !mbar_wait(&bars->dq_sent, (t - 1) & 1, abort_flag)) return false;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int chunk = (cg & 1) * 4 + c;
+      for (int c4 = 0; c4 < 4; ++c4) {
+        const int chunk = (cg & 1) * 4 + c4;
         *reinterpret_cast<uint4*>(dq_row + ((chunk ^ (row & 7)) << 4)) =
-            make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+            make_uint4(o[4 * c4], o[4 * c4 + 1], o[4 * c4 + 2], o[4 * c4 + 3]);
       }
       fence_proxy_async_smem();
-      mbar_arrive(&bars->dq_staged[b]);
+      mbar_arrive(&bars->dq_staged);
       return true;
     };
-
-    // per-row scalars, fetched one tile ahead: their loads share the SM's path to L2 with the dQ
-    // reduce traffic and would otherwise stall the arithmetic. Queries beyond S contribute
-    // nothing (p = exp2(-inf) = 0).
-    auto load_row = [&](int i, float& l2, float& dl) {
-      const int qq = (kt + i) * kFT + row;
-      const bool in = i < n_it && qq < S;
-      l2 = in ? lse[vec_base + qq] * kFLog2e : INFINITY;
-      dl = in ? delta[vec_base + qq] : 0.f;
-    };
-    float next_lse2, next_delta;
-    load_row(0, next_lse2, next_delta);
-
-    for (int i = 0; i < n_it; ++i) {
-      const int q0 = (kt + i) * kFT;
-      const int q = q0 + row;
-      const bool diagonal = (i == 0);
-      const float row_lse2 = next_lse2, row_delta = next_delta;
-      load_row(i + 1, next_lse2, next_delta);
-      if (warp == 2) DAD_TRACE(0);
-      if (warp == 17) DAD_TRACE(2);
-      if (!(ok = mbar_wait(&bars->x_full, i & 1, abort_flag))) break;
-      if (warp == 2) DAD_TRACE(0);
-      tc_fence_after_sync();
-      uint32_t x1[32], x2[32];
-      tmem_ld32(tlane + kColS + cg * 32, x1);
-      tmem_ld32(tlane + kColDP + cg * 32, x2);
-      tmem_wait_ld();
-      tc_fence_before_sync();
-      mbar_arrive(&bars->x_free);  // scores are in registers: the next tile's GEMMs may overwrite
-      if (warp == 2) DAD_TRACE(0);
-
-      // The arithmetic runs out of registers while the tensor core is still busy with tile i-1.
-      uint32_t pw[16], dw[16];
+    // dK / dV of a finished item: tensor memory -> bf16 rows in the item's own K / V buffers
+    // (every GEMM that read them has completed), from where the reducer warp stores them. cg 0,1
+    // hold dV columns [32 (cg & 1), +32), cg 2,3 dK likewise; sixteen columns at a time.
+    auto stage_dkv = [&](int kb) {
+      uint8_t* dst = smem + (cg < 2 ? L::kV : L::kK) + kb * kFPanel + row * 128;
 #pragma unroll
-      for (int c = 0; c < 32; c += 2) {
-        float pv[2], dv2[2];
+      for (int h = 0; h < 2; ++h) {
+        uint32_t o[16];
+        tmem_ld16(tlane + (cg < 2 ? kColDV : kColDK) + (cg & 1) * 32 + h * 16, o);
+        tmem_wait_ld();
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int key = k0 + cg * 32 + c + e;
-          float p = ex2(fmaf(__uint_as_float(x1[c + e]), scale_log2, -row_lse2));
-          if (diagonal && key > q) p = 0.f;
-          float g = __uint_as_float(x2[c + e]);
-          float pd = p;
-          if (DROP) {
-            const uint64_t idx = (static_cast<uint64_t>(unit0 + bh) * S + q) * S + key;
-            const float mk = (p != 0.f && philox_keep(rng, idx, rate)) ? keep_scale : 0.f;
-            pd = p * mk;
-            g *= mk;
-          }
-          pv[e] = pd;
-          dv2[e] = p * (g - row_delta) * scale;
-        }
-        pw[c / 2] = pack_bf16(pv[0], pv[1]);
-        dw[c / 2] = pack_bf16(dv2[0], dv2[1]);
-      }
-      if (warp == 2) DAD_TRACE(0);
-      // P / dS of tile i-1 consumed and its dQ complete in tensor memory
-      if (i > 0) {
-        if (!(ok = mbar_wait(&bars->acc_done, (i - 1) & 1, abort_flag))) break;
-        tc_fence_after_sync();
-      }
-      if (warp == 2) DAD_TRACE(0);
-#pragma unroll
-      for (int v4 = 0; v4 < 4; ++v4) {
-        const int chunk = (cg & 1) * 4 + v4;  // 16-byte chunk within the 128-byte row of the panel
-        const int off = (chunk ^ (row & 7)) << 4;
-        *reinterpret_cast<uint4*>(p_row + off) =
-            make_uint4(pw[4 * v4], pw[4 * v4 + 1], pw[4 * v4 + 2], pw[4 * v4 + 3]);
-        *reinterpret_cast<uint4*>(ds_row + off) =
-            make_uint4(dw[4 * v4], dw[4 * v4 + 1], dw[4 * v4 + 2], dw[4 * v4 + 3]);
-      }
-      fence_proxy_async_smem();
-      mbar_arrive(&bars->w_full);
-      if (warp == 2) DAD_TRACE(0);
-      if (warp == 17) DAD_TRACE(2);
-      if (i > 0 && !(ok = drain_dq(i - 1))) break;
-    }
-
-    // last tile's dQ, then dK / dV
-    if (ok) ok = mbar_wait(&bars->acc_done, (n_it - 1) & 1, abort_flag);
-    tc_fence_after_sync();
-    if (ok) ok = drain_dq(n_it - 1);
-    if (ok) {
-      // cg 0,1 store dV columns [32 cg', +32), cg 2,3 store dK columns likewise
-      const int key = k0 + row;
-      const uint32_t col = (cg < 2 ? kColDV : kColDK) + (cg & 1) * 32;
-      __nv_bfloat16* dst = (cg < 2 ? dv : dk) + (vec_base + key) * D + (cg & 1) * 32;
-      uint32_t o[32];
-      tmem_ld32(tlane + col, o);
-      tmem_wait_ld();
-      if (key < S) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          *reinterpret_cast<uint4*>(dst + i * 8) = make_uint4(
+        for (int i = 0; i < 2; ++i) {
+          const int chunk = (cg & 1) * 4 + h * 2 + i;
+          *reinterpret_cast<uint4*>(dst + ((chunk ^ (row & 7)) << 4)) = make_uint4(
               pack_bf16(__uint_as_float(o[8 * i + 0]), __uint_as_float(o[8 * i + 1])),
               pack_bf16(__uint_as_float(o[8 * i + 2]), __uint_as_float(o[8 * i + 3])),
               pack_bf16(__uint_as_float(o[8 * i + 4]), __uint_as_float(o[8 * i + 5])),
               pack_bf16(__uint_as_float(o[8 * i + 6]), __uint_as_float(o[8 * i + 7])));
+        }
+      }
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+      mbar_arrive(&bars->dkv_staged);
+    };
+    // per-row scalars, fetched one tile ahead: their loads share the SM's path to L2 with the dQ
+    // reduce traffic and would otherwise stall the arithmetic. Queries beyond S contribute
+    // nothing (p = exp2(-inf) = 0).
+    auto load_row = [&](bool valid, int q_tile, int bh, float& l2, float& dl) {
+      const int qq = q_tile * kFT + row;
+      const bool in = valid && qq < S;
+      const size_t at = static_cast<size_t>(bh) * S + qq;
+      l2 = in ? lse[at] * kFLog2e : INFINITY;
+      dl = in ? delta[at] : 0.f;
+    };
+
+    ItemFeed feed{bars, abort_flag, 0};
+    int cur = feed.fetch(n_items);
+    int nxt = cur < n_items ? feed.fetch(n_items) : n_items;
+    float next_lse2 = INFINITY, next_delta = 0.f;
+    if (cur < n_items) {
+      const Item t0 = decode_item(cur, BH, n_tiles, group_bh);
+      load_row(true, t0.kt, t0.bh, next_lse2, next_delta);
+    }
+    int g = 0, j = 0;
+
+    for (; ok && cur < n_items; ++j) {
+      const Item t = decode_item(cur, BH, n_tiles, group_bh);
+      const int k0 = t.kt * kFT;
+      for (int i = 0; i < t.n_it; ++i, ++g) {
+        const int q = (t.kt + i) * kFT + row;
+        const bool diagonal = (i == 0);
+        const bool new_item = (i == 0 && j > 0);  // the item before this one is complete
+        const float row_lse2 = next_lse2, row_delta = next_delta;
+        if (i + 1 < t.n_it) {
+          load_row(true, t.kt + i + 1, t.bh, next_lse2, next_delta);
+        } else {
+          const Item tn = decode_item(nxt < n_items ? nxt : 0, BH, n_tiles, group_bh);
+          load_row(nxt < n_items, tn.kt, tn.bh, next_lse2, next_delta);
+        }
+        if (warp == 2) DAD_TRACE(0);
+        if (!(ok = mbar_wait(&bars->x_full, g & 1, abort_flag))) break;
+        if (warp == 2) DAD_TRACE(0);
+        tc_fence_after_sync();
+        // Sixteen columns at a time: the packed results have to wait in registers for the P / dS
+        // buffers, and nothing here may spill (local memory shares the path the reduce-adds load).
+        uint32_t pw[16], dw[16];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t x1[16], x2[16];
+          tmem_ld16(tlane + kColS + cg * 32 + h * 16, x1);
+          tmem_ld16(tlane + kColDP + cg * 32 + h * 16, x2);
+          tmem_wait_ld();
+          if (h == 1) {
+            tc_fence_before_sync();
+            mbar_arrive(&bars->x_free);  // scores are in registers: the next tile's GEMMs may overwrite
+            if (warp == 2) DAD_TRACE(0);
+          }
+#pragma unroll
+          for (int cc = 0; cc < 16; cc += 2) {
+            float pv[2], dv2[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int key = k0 + cg * 32 + h * 16 + cc + e;
+              float p = ex2(fmaf(__uint_as_float(x1[cc + e]), scale_log2, -row_lse2));
+              if (diagonal && key > q) p = 0.f;
+              float gr = __uint_as_float(x2[cc + e]);
+              float pd = p;
+              if (DROP) {
+                const uint64_t idx = (static_cast<uint64_t>(unit0 + t.bh) * S + q) * S + key;
+                const float mk = (p != 0.f && philox_keep(rng, idx, rate)) ? keep_scale : 0.f;
+                pd = p * mk;
+                gr *= mk;
+              }
+              pv[e] = pd;
+              dv2[e] = p * (gr - row_delta) * scale;
+            }
+            pw[h * 8 + cc / 2] = pack_bf16(pv[0], pv[1]);
+            dw[h * 8 + cc / 2] = pack_bf16(dv2[0], dv2[1]);
+          }
+        }
+        if (warp == 2) DAD_TRACE(0);
+        // P / dS of tile g-1 consumed and its dQ complete in tensor memory
+        if (g > 0) {
+          if (!(ok = mbar_wait(&bars->acc_done, (g - 1) & 1, abort_flag))) break;
+          tc_fence_after_sync();
+        }
+        if (warp == 2) DAD_TRACE(0);
+        // Across an item boundary tile g-1 also completed dK / dV of the previous item: take them
+        // out of tensor memory before w_full lets this item's first GEMMs overwrite them.
+        if (new_item) stage_dkv((j - 1) & 1);
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) {
+          const int chunk = (cg & 1) * 4 + v4;  // 16-byte chunk within the 128-byte row of the panel
+          const int off = (chunk ^ (row & 7)) << 4;
+          *reinterpret_cast<uint4*>(p_row + off) =
+              make_uint4(pw[4 * v4], pw[4 * v4 + 1], pw[4 * v4 + 2], pw[4 * v4 + 3]);
+          *reinterpret_cast<uint4*>(ds_row + off) =
+              make_uint4(dw[4 * v4], dw[4 * v4 + 1], dw[4 * v4 + 2], dw[4 * v4 + 3]);
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&bars->w_full);
+        if (warp == 2) DAD_TRACE(0);
+        if (g > 0 && !(ok = drain_dq(g - 1))) break;
+      }
+      cur = nxt;
+      nxt = (ok && cur < n_items) ? feed.fetch(n_items) : n_items;
+    }
+
+    // the last item's dK / dV and its last tile's dQ
+    if (ok && g > 0) {
+      ok = mbar_wait(&bars->acc_done, (g - 1) & 1, abort_flag);
+      tc_fence_after_sync();
+      if (ok) {
+        stage_dkv((j - 1) & 1);
+        ok = drain_dq(g - 1);
       }
     }
   }
@@ -415,12 +569,14 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 // delta[r] = sum_d dO[r,d] O[r,d] (reference flash_delta_kernel, cuda/attention.cu:76-85) and the
 // zero fill of the fp32 dQ workspace, in one pass over the rows.
 __global__ void fused_prepare_kernel(float* __restrict__ delta, float* __restrict__ dq_ws,
+                                     int* __restrict__ item_counter,
                                      const __nv_bfloat16* __restrict__ dout,
                                      const __nv_bfloat16* __restrict__ out, int64_t rows) {
   constexpr int D = kFD, Lr = D / 8;  // 8 lanes per row
   pdl_wait();
   pdl_launch_dependents();
   const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t == 0) *item_counter = 0;
   const int64_t r = t / Lr;
   const int c = static_cast<int>(t % Lr) * 8;
   float sum = 0.f;
@@ -487,10 +643,12 @@ int make_dq_workspace_map(CUtensorMap* map, float* ws, int BH, int S) {
 DAD_TRACE_READER(dadattn_trace_read_fused)
 namespace dadattn {
 
-// Workspace: delta [BH,S] fp32, then the dQ accumulator [BH,S,64] fp32 (256-byte aligned).
+// Workspace: delta [BH,S] fp32, then the dQ accumulator [BH,S,64] fp32 (256-byte aligned), then
+// 256 bytes that hold the work-item counter.
 size_t fused_bwd_workspace_bytes(int BH, int S) {
   const size_t delta_bytes = (static_cast<size_t>(BH) * S * sizeof(float) + 255) / 256 * 256;
-  return delta_bytes + static_cast<size_t>(BH) * S * kFD * sizeof(float);
+  const size_t dq_bytes = (static_cast<size_t>(BH) * S * kFD * sizeof(float) + 255) / 256 * 256;
+  return delta_bytes + dq_bytes + 256;
 }
 
 int launch_bwd_fused_d64(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspace, const uint16_t* dout,
@@ -498,14 +656,18 @@ int launch_bwd_fused_d64(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspa
                          const uint16_t* v, int BH, int S, float scale, float rate, uint64_t seed,
                          uint64_t offset, int64_t unit0, cudaStream_t st) {
   using BF = __nv_bfloat16;
+  const size_t delta_bytes = (static_cast<size_t>(BH) * S * sizeof(float) + 255) / 256 * 256;
+  const size_t dq_bytes = (static_cast<size_t>(BH) * S * kFD * sizeof(float) + 255) / 256 * 256;
   float* delta = static_cast<float*>(workspace);
-  float* dq_ws = reinterpret_cast<float*>(static_cast<char*>(workspace) +
-                                          (static_cast<size_t>(BH) * S * sizeof(float) + 255) / 256 * 256);
-  CUtensorMap mq, mk, mv, mdo, mws;
+  float* dq_ws = reinterpret_cast<float*>(static_cast<char*>(workspace) + delta_bytes);
+  int* item_counter = reinterpret_cast<int*>(static_cast<char*>(workspace) + delta_bytes + dq_bytes);
+  CUtensorMap mq, mk, mv, mdo, mws, mdk, mdv;
   if (int rc = make_tensor_map_bf16(&mq, q, BH, S, kFD, kFT)) return rc;
   if (int rc = make_tensor_map_bf16(&mk, k, BH, S, kFD, kFT)) return rc;
   if (int rc = make_tensor_map_bf16(&mv, v, BH, S, kFD, kFT)) return rc;
   if (int rc = make_tensor_map_bf16(&mdo, dout, BH, S, kFD, kFT)) return rc;
+  if (int rc = make_tensor_map_bf16(&mdk, dk, BH, S, kFD, kFT)) return rc;
+  if (int rc = make_tensor_map_bf16(&mdv, dv, BH, S, kFD, kFT)) return rc;
   if (int rc = make_dq_workspace_map(&mws, dq_ws, BH, S)) return rc;
   int* status = device_status_word();
   if (!status) return DADATTN_E_CUDA;
@@ -514,17 +676,27 @@ int launch_bwd_fused_d64(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspa
   const int64_t prep_threads = rows * (kFD / 8);
   stage_event(0, st);
   DAD_CUDA(launch_pdl(fused_prepare_kernel, dim3(static_cast<unsigned>((prep_threads + 255) / 256)),
-                      dim3(256), 0, st, delta, dq_ws, reinterpret_cast<const BF*>(dout),
+                      dim3(256), 0, st, delta, dq_ws, item_counter, reinterpret_cast<const BF*>(dout),
                       reinterpret_cast<const BF*>(out), rows));
   stage_event(1, st);
   const PhiloxKey rng = make_philox(seed, offset);
-  dim3 grid((S + kFT - 1) / kFT, BH);
+  // One persistent CTA per SM; the CTAs draw (key tile, batch x head) items from a counter.
+  // Batch x head units are worked on in groups whose Q, dO and dQ rows (1 KiB per query) stay
+  // well inside L2.
+  const int64_t n_items = static_cast<int64_t>((S + kFT - 1) / kFT) * BH;
+  if (n_items > INT32_MAX / 2) return fail(DADATTN_E_UNSUPPORTED, "too many (key tile, batch x head) items");
+  int dev = 0, sms = 0;
+  DAD_CUDA(cudaGetDevice(&dev));
+  DAD_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  dim3 grid(static_cast<unsigned>(n_items < sms ? n_items : sms));
+  int group_bh = 65536 / S;
+  group_bh = group_bh < 1 ? 1 : (group_bh > 64 ? 64 : group_bh);
   const bool drop = rate > 0.f;
   auto kern = drop ? flash_bwd_fused_kernel<true> : flash_bwd_fused_kernel<false>;
   DAD_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FusedSmem::kBytes));
-  DAD_CUDA(launch_pdl(kern, grid, dim3(kFThreads), FusedSmem::kBytes, st, mq, mk, mv, mdo, mws,
-                      reinterpret_cast<BF*>(dk), reinterpret_cast<BF*>(dv), lse,
-                      static_cast<const float*>(delta), S, scale, rate, rng, unit0, status));
+  DAD_CUDA(launch_pdl(kern, grid, dim3(kFThreads), FusedSmem::kBytes, st, mq, mk, mv, mdo, mws, mdk, mdv,
+                      lse, static_cast<const float*>(delta), item_counter, BH, S, group_bh, scale, rate,
+                      rng, unit0, status));
   stage_event(2, st);
   const int64_t n8 = rows * kFD / 8;
   DAD_CUDA(launch_pdl(fused_convert_kernel, dim3(static_cast<unsigned>((n8 + 255) / 256)), dim3(256), 0,
