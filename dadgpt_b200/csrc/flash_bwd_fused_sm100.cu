@@ -469,7 +469,7 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int q = (t.kt + i) * kFT + row;
         const bool diagonal = (i == 0);
         const bool new_item = (i == 0 && j > 0);  // the item before this one is complete
-        const float row_lse2 = next_lse2, row_delta = next_delta;
+        const float row_lse2 = next_lse2, row_delta_s = next_delta * scale;
         if (i + 1 < t.n_it) {
           load_row(true, t.kt + i + 1, t.bh, next_lse2, next_delta);
         } else {
@@ -494,27 +494,40 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_arrive(&bars->x_free);  // scores are in registers: the next tile's GEMMs may overwrite
             if (warp == 2) DAD_TRACE(0);
           }
-#pragma unroll
-          for (int cc = 0; cc < 16; cc += 2) {
-            float pv[2], dv2[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int key = k0 + cg * 32 + h * 16 + cc + e;
-              float p = ex2(fmaf(__uint_as_float(x1[cc + e]), scale_log2, -row_lse2));
-              if (diagonal && key > q) p = 0.f;
-              float gr = __uint_as_float(x2[cc + e]);
-              float pd = p;
-              if (DROP) {
-                const uint64_t idx = (static_cast<uint64_t>(unit0 + t.bh) * S + q) * S + key;
-                const float mk = (p != 0.f && philox_keep(rng, idx, rate)) ? keep_scale : 0.f;
-                pd = p * mk;
-                gr *= mk;
-              }
-              pv[e] = pd;
-              dv2[e] = p * (gr - row_delta) * scale;
+          // ds = p (dP - delta) scale as p * fma(dP, scale, -delta scale); the causal compare
+          // only exists on an item's first (diagonal) tile
+          auto elem = [&](int cc, bool masked, float& pd, float& ds) {
+            const int key = k0 + cg * 32 + h * 16 + cc;
+            float p = ex2(fmaf(__uint_as_float(x1[cc]), scale_log2, -row_lse2));
+            if (masked && key > q) p = 0.f;
+            float gr = __uint_as_float(x2[cc]);
+            pd = p;
+            if (DROP) {
+              const uint64_t idx = (static_cast<uint64_t>(unit0 + t.bh) * S + q) * S + key;
+              const float mk = (p != 0.f && philox_keep(rng, idx, rate)) ? keep_scale : 0.f;
+              pd = p * mk;
+              gr *= mk;
             }
-            pw[h * 8 + cc / 2] = pack_bf16(pv[0], pv[1]);
-            dw[h * 8 + cc / 2] = pack_bf16(dv2[0], dv2[1]);
+            ds = p * fmaf(gr, scale, -row_delta_s);
+          };
+          if (diagonal) {
+#pragma unroll
+            for (int cc = 0; cc < 16; cc += 2) {
+              float p0, p1, d0, d1;
+              elem(cc, true, p0, d0);
+              elem(cc + 1, true, p1, d1);
+              pw[h * 8 + cc / 2] = pack_bf16(p0, p1);
+              dw[h * 8 + cc / 2] = pack_bf16(d0, d1);
+            }
+          } else {
+#pragma unroll
+            for (int cc = 0; cc < 16; cc += 2) {
+              float p0, p1, d0, d1;
+              elem(cc, false, p0, d0);
+              elem(cc + 1, false, p1, d1);
+              pw[h * 8 + cc / 2] = pack_bf16(p0, p1);
+              dw[h * 8 + cc / 2] = pack_bf16(d0, d1);
+            }
           }
         }
         if (warp == 2) DAD_TRACE(0);
@@ -567,18 +580,26 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 }
 
 // delta[r] = sum_d dO[r,d] O[r,d] (reference flash_delta_kernel, cuda/attention.cu:76-85) and the
-// zero fill of the fp32 dQ workspace, in one pass over the rows.
+// zero fill of the fp32 dQ workspace, in one pass over the rows. The zero fill does not depend on
+// the kernel before this one in the stream (normally the forward pass), so it runs ahead of the
+// dependency wait and overlaps that kernel's tail. The only kernel that reads the workspace,
+// fused_convert_kernel, releases its dependents after its reads.
 __global__ void fused_prepare_kernel(float* __restrict__ delta, float* __restrict__ dq_ws,
                                      int* __restrict__ item_counter,
                                      const __nv_bfloat16* __restrict__ dout,
                                      const __nv_bfloat16* __restrict__ out, int64_t rows) {
   constexpr int D = kFD, Lr = D / 8;  // 8 lanes per row
-  pdl_wait();
-  pdl_launch_dependents();
   const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (t == 0) *item_counter = 0;
   const int64_t r = t / Lr;
   const int c = static_cast<int>(t % Lr) * 8;
+  if (r < rows) {
+    float4* z = reinterpret_cast<float4*>(dq_ws + r * D + c);
+    z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (t == 0) *item_counter = 0;
+  pdl_wait();
+  pdl_launch_dependents();
   float sum = 0.f;
   if (r < rows) {
     const uint4 a = *reinterpret_cast<const uint4*>(dout + r * D + c);
@@ -589,26 +610,27 @@ __global__ void fused_prepare_kernel(float* __restrict__ delta, float* __restric
       sum = fmaf(__uint_as_float(aw[i] << 16), __uint_as_float(bw[i] << 16), sum);
       sum = fmaf(__uint_as_float(aw[i] & 0xffff0000u), __uint_as_float(bw[i] & 0xffff0000u), sum);
     }
-    float4* z = reinterpret_cast<float4*>(dq_ws + r * D + c);
-    z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
-    z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
 #pragma unroll
   for (int o = Lr / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
   if (r < rows && c == 0) delta[r] = sum;
 }
 
-// dQ workspace (fp32) -> dq (bf16)
+// dQ workspace (fp32) -> dq (bf16). Dependents are released only after the workspace has been
+// read: the next backward call's prepare kernel clears it ahead of its own dependency wait.
 __global__ void fused_convert_kernel(__nv_bfloat16* __restrict__ dq, const float* __restrict__ dq_ws,
                                      int64_t n8) {
   pdl_wait();
-  pdl_launch_dependents();
   const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (t >= n8) return;
-  const float4 a = *reinterpret_cast<const float4*>(dq_ws + t * 8);
-  const float4 b = *reinterpret_cast<const float4*>(dq_ws + t * 8 + 4);
-  *reinterpret_cast<uint4*>(dq + t * 8) = make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w),
-                                                     pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+  if (t < n8) {
+    a = *reinterpret_cast<const float4*>(dq_ws + t * 8);
+    b = *reinterpret_cast<const float4*>(dq_ws + t * 8 + 4);
+  }
+  // the loads have returned once their values are used; keep the trigger behind that use
+  const uint4 w = make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
+  if (t < n8) *reinterpret_cast<uint4*>(dq + t * 8) = w;
+  pdl_launch_dependents();
 }
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
