@@ -132,6 +132,10 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+#ifdef DADATTN_TRACE
+  int life_n_ = 0;
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_trace[3][life_n_++] = clock64();
+#endif
   const int qt = gridDim.x - 1 - blockIdx.x;  // heaviest tiles first
   const int bh = blockIdx.y;
   const int q0 = qt * kBM;
@@ -173,6 +177,9 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
   // may have produced. Once every CTA of this grid is here the next grid may start its set-up.
   pdl_wait();
   pdl_launch_dependents();
+#ifdef DADATTN_TRACE
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_trace[3][life_n_++] = clock64();
+#endif
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -458,6 +465,9 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
   // ------------------------------ common exit ------------------------------
   tc_fence_before_sync();
   __syncthreads();
+#ifdef DADATTN_TRACE
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_trace[3][life_n_++] = clock64();
+#endif
   if (warp == 1) {
     __syncwarp();
     tc_fence_after_sync();
