@@ -183,9 +183,10 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    if args.decode_only:
+    if args.decode_only or args.decode_full:
         d = bench_decode(dad, W, dev, world, barrier, max_over_ranks, torch,
-                         steps=args.steps, graph=False)
+                         steps=None if args.decode_full else args.steps,
+                         graph=args.decode_full)
         if rank == 0:
             print(json.dumps(d), flush=True)
         return
@@ -491,6 +492,8 @@ def main():
                     help="only the fwd+bwd timed region (for ncu captures of a small run)")
     ap.add_argument("--decode-only", action="store_true",
                     help="only the KV-cache decode workload (for ncu captures)")
+    ap.add_argument("--decode-full", action="store_true",
+                    help="only the KV-cache decode workload, all 256 steps, one CUDA graph per step")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
