@@ -12,8 +12,10 @@ from .attention import (  # noqa: F401
     dropout_mask,
     gpu_flash_attention_backward,
     gpu_flash_attention_backward_bf16,
+    gpu_flash_attention_backward_via_bf16,
     gpu_flash_attention_forward,
     gpu_flash_attention_forward_bf16,
+    gpu_flash_attention_forward_via_bf16,
     gpu_flash_attention_supported,
 )
 

@@ -26,6 +26,12 @@ SIGNATURES = {
     "dadattn_flash_bwd_bf16": (I, [P, P, P, P, SZ, P, P, P, P, P, P, I, I, I, F, F, U64, U64, I64, P]),
     "dadattn_set_bwd_deterministic": (I, [I]),
     "dadattn_set_stage_events": (I, [P, I]),
+    "dadattn_flash_f32_via_bf16_workspace_bytes": (SZ, [I, I, I]),
+    "dadattn_flash_fwd_f32_via_bf16": (I, [P, P, P, P, P, I, I, I, F, P, SZ, P]),
+    "dadattn_flash_bwd_f32_via_bf16": (I, [P] * 9 + [I, I, I, F, P, SZ, P]),
+    "dadattn_set_f32_precision": (I, [I]),
+    "dadattn_get_f32_precision": (I, []),
+    "dadattn_library_scratch": (I, [SZ, P]),
     "dadattn_decode_f32": (I, [P] * 6 + [I, I, I, I, F, P]),
     "dadattn_decode_workspace_bytes": (SZ, [I, I, I, I]),
     "dadattn_decode_bf16": (I, [P] * 7 + [I, I, I, I, F, P, SZ, P]),

@@ -95,6 +95,38 @@ def gpu_flash_attention_backward_bf16(dq, dk, dv, workspace, dout, out, lse, q, 
         _ptr(q), _ptr(k), _ptr(v), BH, S, d_head, scale, rate, seed, offset, unit0, _stream()))
 
 
+def flash_f32_via_bf16_workspace_bytes(BH, S, d_head) -> int:
+    return int(_lib.load().dadattn_flash_f32_via_bf16_workspace_bytes(BH, S, d_head))
+
+
+def gpu_flash_attention_forward_via_bf16(out, lse, q, k, v, BH, S, d_head, scale, workspace):
+    """fp32 tensors, bf16 tensor-core arithmetic: what the reference's fp32 signature
+    (cuda/attention.cu:234-239) computes when its GEMM precision is BF16 (cuda/gpu_ops.cuh:43-44)."""
+    lib = _lib.load()
+    for n, t in (("out", out), ("q", q), ("k", k), ("v", v)):
+        _need(t, torch.float32, (BH, S, d_head), n)
+    _need(lse, torch.float32, (BH, S), "lse")
+    nbytes = workspace.numel() * workspace.element_size()
+    _lib.check(lib.dadattn_flash_fwd_f32_via_bf16(_ptr(out), _ptr(lse), _ptr(q), _ptr(k), _ptr(v),
+                                                  BH, S, d_head, scale, _ptr(workspace), nbytes,
+                                                  _stream()))
+
+
+def gpu_flash_attention_backward_via_bf16(dq, dk, dv, dout, out, lse, q, k, v, BH, S, d_head, scale,
+                                          workspace):
+    """Backward of the call above (reference cuda/attention.cu:241-252; no ``delta`` argument:
+    the workspace holds it)."""
+    lib = _lib.load()
+    for n, t in (("dq", dq), ("dk", dk), ("dv", dv), ("dout", dout), ("out", out), ("q", q),
+                 ("k", k), ("v", v)):
+        _need(t, torch.float32, (BH, S, d_head), n)
+    _need(lse, torch.float32, (BH, S), "lse")
+    nbytes = workspace.numel() * workspace.element_size()
+    _lib.check(lib.dadattn_flash_bwd_f32_via_bf16(
+        _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dout), _ptr(out), _ptr(lse), _ptr(q), _ptr(k), _ptr(v),
+        BH, S, d_head, scale, _ptr(workspace), nbytes, _stream()))
+
+
 def set_backward_deterministic(on: bool) -> None:
     """Head size 64: choose between the single-pass backward (default; dQ summed across key tiles
     in arrival order, so its last bits may vary between runs) and the two-kernel backward that,

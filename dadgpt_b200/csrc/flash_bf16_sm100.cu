@@ -99,7 +99,6 @@ struct FwdSmem {
   // SM's shared-memory bandwidth, so every byte of P kept out of shared memory counts).
   // D = 64: one bf16 tile in shared memory.
   static constexpr bool kPTmem = D == 128;
-  static constexpr int kPBufs = 1;
   static constexpr int kBars = kP + (kPTmem ? 0 : 2 * kPanelBytes);
   static constexpr int kBytes = kBars + 256;
 };

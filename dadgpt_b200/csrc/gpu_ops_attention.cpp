@@ -3,6 +3,11 @@
 // dadattn C ABI. Link this (and libdadattn) in place of cuda/attention.cu and the reference's
 // src/model.cpp, src/train.cpp and src/generate.cpp build and run unchanged.
 //
+// Precision: with dadattn_set_f32_precision(1) (or DADATTN_PRECISION=bf16 in the environment)
+// head size 64 runs on the bf16 tensor-core kernels, operands rounded on the fly as the
+// reference's own GEMMs do under gpu_set_matmul_precision(BF16); the workspace that needs comes
+// from the library's grow-only scratch buffer, since these signatures cannot carry one.
+//
 // Behaviour kept from the reference: work is enqueued on the legacy default stream without
 // synchronising; a head size outside {32, 64} and any CUDA error surface as std::runtime_error
 // (cuda/attention.cu:238,251; CUDA_CHECK in cuda/gpu_ops.cuh:10-17).
@@ -13,10 +18,25 @@
 
 bool gpu_flash_attention_supported(int d_head) { return d_head == 32 || d_head == 64; }
 
+namespace {
+// the bf16 kernels want 16-byte aligned tensors; the reference's arena offsets are multiples of
+// B * ctx * d_model floats, which at head size 64 always are
+bool use_tensor_cores(int d_head) { return d_head == 64 && dadattn_get_f32_precision() == 1; }
+}  // namespace
+
 void gpu_flash_attention_forward(float* out, float* lse, const float* q, const float* k,
                                  const float* v, int BH, int S, int d_head, float scale) {
   if (!gpu_flash_attention_supported(d_head))
     throw std::runtime_error("flash attention: unsupported d_head " + std::to_string(d_head));
+  if (use_tensor_cores(d_head)) {
+    const size_t bytes = dadattn_flash_f32_via_bf16_workspace_bytes(BH, S, d_head);
+    void* ws = nullptr;
+    if (dadattn_library_scratch(bytes, &ws) != DADATTN_OK ||
+        dadattn_flash_fwd_f32_via_bf16(out, lse, q, k, v, BH, S, d_head, scale, ws, bytes, nullptr) !=
+            DADATTN_OK)
+      throw std::runtime_error(std::string("CUDA error: ") + dadattn_last_error());
+    return;
+  }
   if (dadattn_flash_fwd_f32(out, lse, q, k, v, BH, S, d_head, scale, nullptr) != DADATTN_OK)
     throw std::runtime_error(std::string("CUDA error: ") + dadattn_last_error());
 }
@@ -27,6 +47,15 @@ void gpu_flash_attention_backward(float* dq, float* dk, float* dv, float* delta,
                                   float scale) {
   if (!gpu_flash_attention_supported(d_head))
     throw std::runtime_error("flash attention: unsupported d_head " + std::to_string(d_head));
+  if (use_tensor_cores(d_head)) {
+    const size_t bytes = dadattn_flash_f32_via_bf16_workspace_bytes(BH, S, d_head);
+    void* ws = nullptr;
+    if (dadattn_library_scratch(bytes, &ws) != DADATTN_OK ||
+        dadattn_flash_bwd_f32_via_bf16(dq, dk, dv, dout, out, lse, q, k, v, BH, S, d_head, scale, ws,
+                                       bytes, nullptr) != DADATTN_OK)
+      throw std::runtime_error(std::string("CUDA error: ") + dadattn_last_error());
+    return;
+  }
   if (dadattn_flash_bwd_f32(dq, dk, dv, delta, dout, out, lse, q, k, v, BH, S, d_head, scale,
                             nullptr) != DADATTN_OK)
     throw std::runtime_error(std::string("CUDA error: ") + dadattn_last_error());

@@ -124,6 +124,44 @@ int dadattn_set_bwd_deterministic(int on);
  * (three events). Events beyond `count` are not recorded. Pass NULL to switch it off. */
 int dadattn_set_stage_events(void** events, int count);
 
+/* ---- fp32 tensors, tensor-core arithmetic ---------------------------------------------------- */
+
+/* The reference keeps activations in fp32 and lowers precision per operation:
+ * gpu_set_matmul_precision(BF16) (reference cuda/gpu_ops.cuh:43-44; the training default,
+ * src/train.hpp:29) makes its GEMMs round operands to bf16 and accumulate in fp32. These calls
+ * give the fused attention the same contract on the reference's own fp32 tensors: operands are
+ * rounded to bf16 into `workspace`, the bf16 tensor-core kernels run (fp32 softmax and
+ * accumulation), results are widened back to fp32; lse is written in fp32 directly. Argument
+ * meaning as dadattn_flash_fwd_f32 / dadattn_flash_bwd_f32 (no `delta`: the workspace holds it).
+ * D must be 64 or 128, scale > 0, tensors 16-byte aligned, workspace 256-byte aligned and at
+ * least dadattn_flash_f32_via_bf16_workspace_bytes(BH,S,D) bytes (its contents need not
+ * survive between calls). No counterpart in the reference, whose fused kernels are fp32 only. */
+size_t dadattn_flash_f32_via_bf16_workspace_bytes(int BH, int S, int D);
+int dadattn_flash_fwd_f32_via_bf16(float* out, float* lse, const float* q, const float* k,
+                                   const float* v, int BH, int S, int D, float scale,
+                                   void* workspace, size_t workspace_bytes,
+                                   dadattn_stream_t stream);
+int dadattn_flash_bwd_f32_via_bf16(float* dq, float* dk, float* dv, const float* dout,
+                                   const float* out, const float* lse, const float* q,
+                                   const float* k, const float* v, int BH, int S, int D,
+                                   float scale, void* workspace, size_t workspace_bytes,
+                                   dadattn_stream_t stream);
+
+/* Process-wide precision of the drop-in symbols gpu_flash_attention_forward / _backward
+ * (libdadattn_gpuops.so): 0 = the exact fp32 kernels (default), 1 = the calls above at head size
+ * 64 (other head sizes stay fp32). A host that calls the reference's
+ * gpu_set_matmul_precision(MatmulPrecision::BF16) calls dadattn_set_f32_precision(1) next to it;
+ * without any call the environment variable DADATTN_PRECISION=bf16 selects 1. */
+int dadattn_set_f32_precision(int mode);
+int dadattn_get_f32_precision(void);
+
+/* A grow-only device buffer owned by the library, one per device, for hosts that have no way to
+ * pass a workspace (the drop-in symbols above: the reference's signatures carry none). Allocates
+ * (cudaMalloc) on first use and when `bytes` exceeds what it holds, after waiting for the
+ * device to finish work on the old buffer; every other library entry point allocates nothing.
+ * The buffer is shared: calls that use it must not overlap on the GPU. */
+int dadattn_library_scratch(size_t bytes, void** ptr);
+
 /* ---- KV-cache decode --------------------------------------------------------------------- */
 
 /* Decode attention of model_forward_cached for ONE sequence on the reference's own cache

@@ -8,12 +8,16 @@
 //      (the bars of tests/test_backward.cpp:432-480), S = 70, batch 2, d_head 64 and 32;
 //   2. prefill + cached decode against a full forward (tests/test_model.cpp:375-414), with the
 //      prefill going through the fused forward.
+//   3. the same model with the drop-in switched to bf16 tensor-core arithmetic
+//      (dadattn_set_f32_precision(1)): fused against materialized at the bf16 bars (logits 2e-2,
+//      gradients 3e-2 relative L2), d_head 64.
 // Exit code 0 = all within tolerance; every figure is printed.
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <vector>
 
+#include "dadattn.h"
 #include "gpu_ops.cuh"
 #include "model.hpp"
 
@@ -57,7 +61,7 @@ RunResult run_once(const ModelConfig& config, AttentionImpl impl, const std::vec
   return r;
 }
 
-bool fused_vs_materialized(int d_model, int heads) {
+bool fused_vs_materialized(int d_model, int heads, bool tensor_cores = false) {
   ModelConfig config = make_config(2, d_model, heads, 80);
   const int batch = 2, seq_len = 70, rows = batch * seq_len;
   std::vector<uint16_t> tokens(rows), targets(rows);
@@ -87,9 +91,11 @@ bool fused_vs_materialized(int d_model, int heads) {
     if (r2 > 1e-12) worst_block = std::max(worst_block, std::sqrt(d2 / r2));
   }
   double rel = std::sqrt(diff_sq / std::max(ref_sq, 1e-20));
-  bool ok = max_logit <= 1e-4 && rel <= 1e-4 && worst_block <= 1e-3;
-  std::printf("fused_vs_materialized d_head=%d: max|dlogit|=%.3g grad_rel_l2=%.3g worst_block=%.3g %s\n",
-              d_model / heads, max_logit, rel, worst_block, ok ? "OK" : "FAIL");
+  bool ok = tensor_cores ? (max_logit <= 2e-2 && rel <= 3e-2)
+                         : (max_logit <= 1e-4 && rel <= 1e-4 && worst_block <= 1e-3);
+  std::printf("fused_vs_materialized d_head=%d%s: max|dlogit|=%.3g grad_rel_l2=%.3g worst_block=%.3g %s\n",
+              d_model / heads, tensor_cores ? " (bf16 tensor cores)" : "", max_logit, rel, worst_block,
+              ok ? "OK" : "FAIL");
   return ok;
 }
 
@@ -139,6 +145,9 @@ int main() {
     ok &= fused_vs_materialized(64, 2);   // d_head 32
     ok &= prefill_then_cached(128, 2);
     ok &= prefill_then_cached(64, 2);
+    dadattn_set_f32_precision(1);
+    ok &= fused_vs_materialized(128, 2, true);
+    dadattn_set_f32_precision(0);
     // a head size the reference's fused path refuses: the model must fall back by itself
     std::printf("supported(48)=%d supported(64)=%d\n", gpu_flash_attention_supported(48) ? 1 : 0,
                 gpu_flash_attention_supported(64) ? 1 : 0);

@@ -2,7 +2,8 @@
 linked against libdadattn_gpuops.so in place of its cuda/attention.cu (oracle/Makefile target
 _ref/ref_model_link_check). Reproduces, at the model level, the relations the reference's tests
 pin for this path: fused == materialized (tests/test_backward.cpp:432-480) and prefill + cached
-decode == full forward (tests/test_model.cpp:375-414), both at 1e-4."""
+decode == full forward (tests/test_model.cpp:375-414), both at 1e-4; and fused == materialized
+once more with the drop-in switched to bf16 tensor-core arithmetic, at the bf16 tolerances."""
 import os
 import subprocess
 
@@ -20,4 +21,5 @@ def test_reference_model_runs_on_our_kernels(cuda):
     print(r.stdout, r.stderr)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "ALL OK" in r.stdout
-    assert r.stdout.count(" OK") >= 4
+    assert r.stdout.count(" OK") >= 5
+    assert "(bf16 tensor cores)" in r.stdout
