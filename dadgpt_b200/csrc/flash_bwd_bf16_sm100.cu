@@ -467,6 +467,13 @@ int launch_bwd_fused_d64(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspa
 thread_local cudaEvent_t* g_stage_events = nullptr;
 thread_local int g_stage_event_count = 0;
 
+// flash_bwd_fused128_sm100.cu
+size_t fused128_bwd_workspace_bytes(int BH, int S);
+int launch_bwd_fused_d128(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspace, const uint16_t* dout,
+                          const uint16_t* out, const float* lse, const uint16_t* q, const uint16_t* k,
+                          const uint16_t* v, int BH, int S, float scale, float rate, uint64_t seed,
+                          uint64_t offset, int64_t unit0, cudaStream_t st);
+
 namespace {
 thread_local int g_deterministic = 0;
 }
@@ -491,6 +498,7 @@ extern "C" size_t dadattn_flash_bwd_bf16_workspace_bytes(int BH, int S, int D) {
   if (BH <= 0 || S <= 0 || D <= 0) return 0;
   // delta [BH,S]; at D = 64 also the fp32 dQ accumulator of the single-pass kernel
   if (D == 64) return fused_bwd_workspace_bytes(BH, S);
+  if (D == 128) return fused128_bwd_workspace_bytes(BH, S);
   return static_cast<size_t>(BH) * S * sizeof(float);
 }
 
@@ -522,12 +530,13 @@ extern "C" int dadattn_flash_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, 
   const bool drop = rate > 0.f;
   if (D == 64 && !g_deterministic) {
     if (!aligned(workspace, 256)) return fail(DADATTN_E_ARG, "backward workspace must be 256-byte aligned");
-    stage_event(0, st);
-    stage_event(1, st);
-    const int rc = launch_bwd_fused_d64(dq, dk, dv, workspace, dout, out, lse, q, k, v, BH, S, scale,
-                                        rate, seed, offset, unit0, st);
-    stage_event(2, st);
-    return rc;
+    return launch_bwd_fused_d64(dq, dk, dv, workspace, dout, out, lse, q, k, v, BH, S, scale, rate,
+                                seed, offset, unit0, st);
+  }
+  if (D == 128 && !g_deterministic) {
+    if (!aligned(workspace, 256)) return fail(DADATTN_E_ARG, "backward workspace must be 256-byte aligned");
+    return launch_bwd_fused_d128(dq, dk, dv, workspace, dout, out, lse, q, k, v, BH, S, scale, rate,
+                                 seed, offset, unit0, st);
   }
 #define DAD_BWD16(DH)                                                                            \
   return drop ? launch_bwd_bf16<DH, true>(dq, dk, dv, delta, dout, out, lse, q, k, v, BH, S,     \

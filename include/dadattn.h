@@ -98,8 +98,8 @@ int dadattn_flash_fwd_bf16(uint16_t* out, float* lse, const uint16_t* q, const u
 /* bf16 form of gpu_flash_attention_backward (reference cuda/attention.cu:241-252). dq,dk,dv bf16,
  * written not accumulated. workspace: caller-owned scratch of at least
  * dadattn_flash_bwd_bf16_workspace_bytes(BH,S,D) bytes, 256-byte aligned (it takes the place of
- * the fp32 call's `delta` scratch and, at head size 64, also holds an fp32 dQ accumulator;
- * contents are overwritten). */
+ * the fp32 call's `delta` scratch and also holds the fp32 dQ accumulator of the single-pass
+ * kernels, 4*BH*S*D bytes; contents are overwritten). */
 size_t dadattn_flash_bwd_bf16_workspace_bytes(int BH, int S, int D);
 int dadattn_flash_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspace,
                            size_t workspace_bytes, const uint16_t* dout, const uint16_t* out,
@@ -108,19 +108,20 @@ int dadattn_flash_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* works
                            uint64_t seed, uint64_t offset, int64_t unit0,
                            dadattn_stream_t stream);
 
-/* At head size 64 the backward is a single-pass kernel that adds each key tile's dQ contribution
- * into an fp32 accumulator in the workspace (TMA reduce-add): about twice as fast, but the order
- * of those additions is not fixed, so dQ may differ in its last bits between runs (dK and dV do
+/* By default the backward is a single-pass kernel (one per head size) that forms the
+ * probabilities once and adds each key tile's dQ contribution into an fp32 accumulator in the
+ * workspace (TMA / bulk reduce-add): about 1.4-2x as fast as recomputing them, but the order of
+ * those additions is not fixed, so dQ may differ in its last bits between runs (dK and dV do
  * not). dadattn_set_bwd_deterministic(1) makes the calling thread use the two-kernel backward,
  * which like the reference (cuda/attention.cu:4-6) accumulates nothing across thread blocks;
- * 0 (the default) restores the single-pass kernel. No counterpart in the reference. */
+ * 0 (the default) restores the single-pass kernels. No counterpart in the reference. */
 int dadattn_set_bwd_deterministic(int on);
 
 /* Measurement aid (no counterpart in the reference): when `events` (an array of `count`
  * cudaEvent_t) is set for the calling thread, dadattn_flash_bwd_bf16 records events[i] on the
  * call's stream before its i-th kernel and one more event after its last kernel. The single-pass
- * backward (head size 64) launches three kernels (delta + workspace clear, the fused gradient
- * kernel, fp32 -> bf16 of dQ: four events); the two-kernel backward launches dQ, then dK/dV
+ * backward launches three kernels (delta and workspace clear, the fused gradient kernel,
+ * fp32 -> bf16 of dQ: four events); the two-kernel backward launches dQ, then dK/dV
  * (three events). Events beyond `count` are not recorded. Pass NULL to switch it off. */
 int dadattn_set_stage_events(void** events, int count);
 

@@ -112,7 +112,7 @@ def bwd(dout, out, lse, tensors, scale, dev, **kw):
 
 @pytest.fixture(params=[False, True], ids=["single_pass", "deterministic"])
 def bwd_mode(request):
-    """Both backward paths of head size 64 (head size 128 has only the two-kernel one)."""
+    """Both backward paths: the single-pass kernels (default) and the two-kernel one."""
     set_backward_deterministic(request.param)
     yield request.param
     set_backward_deterministic(False)
@@ -147,7 +147,7 @@ def test_backward_dropout_against_oracle(cuda, oracle, bwd_mode, D):
     part, _ = bwd(dout[1:], out[1:].contiguous(), lse[1:].contiguous(), [t[1:].contiguous() for t in ts],
                   scale, cuda, unit0=1, **kw)
     for a, b, name in zip(part, grads, ("dq", "dk", "dv")):
-        if name == "dq" and D == 64 and not bwd_mode:  # summed in arrival order: last bits may differ
+        if name == "dq" and not bwd_mode:  # summed in arrival order: last bits may differ
             assert rel_l2(a, b[1:]) <= 1e-2
         else:
             assert np.array_equal(a, b[1:])

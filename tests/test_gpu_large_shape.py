@@ -6,7 +6,8 @@ head-size-64 sequences, where the CPU oracle cannot finish whole tensors in seco
 * every element against the fp32 drop-in kernels run on the same bf16-rounded inputs (the fp32
   kernels are themselves checked against the oracle at 1e-5 / 1e-4 in test_gpu_flash_f32.py);
 * a size-independent property: doubling dO doubles dQ, dK, dV exactly (a power-of-two scale
-  commutes with every rounding on the way) wherever the backward is order-deterministic.
+  commutes with every rounding on the way) wherever the backward is order-deterministic; the
+  single-pass and the two-kernel backward agree.
 
 Tolerances as in the build spec: forward max-abs 2e-2, lse 1e-2, gradients 3e-2 relative L2.
 """
@@ -16,7 +17,8 @@ import torch
 
 import dadgpt_b200 as dad
 from dadgpt_b200 import workloads as W
-from dadgpt_b200.attention import device_status, flash_backward_bf16_workspace_bytes
+from dadgpt_b200.attention import (device_status, flash_backward_bf16_workspace_bytes,
+                                   set_backward_deterministic)
 from tests.gpu_util import max_abs, rel_l2
 
 pytestmark = pytest.mark.gpu
@@ -83,12 +85,26 @@ def test_large_shape_T8192_D128(cuda, oracle):
         for got, want, name in zip(grads, g32, ("dq", "dk", "dv")):
             assert rel_l2(got[units].float().cpu().numpy(), want.cpu().numpy()) <= 3e-2, (u0, name)
 
-    # doubling dO doubles the gradients bit for bit (two-kernel backward: no unordered sums)
+    # doubling dO doubles the gradients bit for bit wherever nothing is summed in arrival order:
+    # dK and dV of the single-pass backward, and everything in the two-kernel backward
     g2 = [torch.empty_like(q) for _ in range(3)]
     dad.gpu_flash_attention_backward_bf16(*g2, ws, do * 2, out, lse, q, k, v, BH, S, D, shape.scale)
     assert device_status() == 0
-    for a, b, name in zip(grads, g2, ("dq", "dk", "dv")):
+    assert torch.equal(grads[1] * 2, g2[1]) and torch.equal(grads[2] * 2, g2[2])
+    assert rel_l2((grads[0] * 2).float().cpu().numpy(), g2[0].float().cpu().numpy()) <= 1e-2
+    set_backward_deterministic(True)
+    try:
+        d1 = [torch.empty_like(q) for _ in range(3)]
+        dad.gpu_flash_attention_backward_bf16(*d1, ws, do, out, lse, q, k, v, BH, S, D, shape.scale)
+        dad.gpu_flash_attention_backward_bf16(*g2, ws, do * 2, out, lse, q, k, v, BH, S, D, shape.scale)
+    finally:
+        set_backward_deterministic(False)
+    assert device_status() == 0
+    for a, b, name in zip(d1, g2, ("dq", "dk", "dv")):
         assert torch.equal(a * 2, b), name
+    # and the two backward paths agree
+    for a, b, name in zip(grads, d1, ("dq", "dk", "dv")):
+        assert rel_l2(a.float().cpu().numpy(), b.float().cpu().numpy()) <= 1e-2, name
 
 
 @pytest.mark.parametrize("S", [4096, 4000])
