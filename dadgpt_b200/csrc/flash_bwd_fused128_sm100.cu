@@ -18,8 +18,8 @@
 // workspace happen in whatever order the CTAs reach them, so dQ may differ in its last bits from
 // run to run; dadattn_set_bwd_deterministic(1) selects the two-kernel path.
 //   warp 0      TMA producer          warp 1      MMA issuer + TMEM owner
-//   warps 2-9   compute: two warps per TMEM lane quadrant, each taking 32 of the 64 query columns
-//   warp 10     dQ reducer
+//   warps 2-17  compute: four warps per TMEM lane quadrant, each taking 16 of the 64 query columns
+//   warp 18     dQ reducer
 #include <cuda_bf16.h>
 
 #include <cfloat>
@@ -38,8 +38,8 @@ constexpr int kGSub = 64;                  // queries per step
 constexpr int kGPanel = 128 * 128;         // [128 rows][64 bf16] swizzled panel
 constexpr int kGSubPanel = 64 * 128;       // [64 rows][64 bf16] swizzled panel
 constexpr int kGStages = 3;                // streamed-tile ring depth
-constexpr int kGThreads = 11 * 32;
-constexpr int kGCompute = 8 * 32;
+constexpr int kGThreads = 19 * 32;
+constexpr int kGCompute = 16 * 32;
 constexpr int kGDqTileBytes = kGD * kGSub * 4;   // one dQ^T tile, fp32
 constexpr float kGLog2e = 1.4426950408889634f;
 
@@ -53,8 +53,8 @@ struct G128Smem {
   static constexpr int kDS = kDO + kGStages * kSubTile;  // [128 keys][64 q] bf16, one panel
   static constexpr int kP = kDS + kGPanel;
   static constexpr int kDQ = kP + kGPanel;               // [128 dims][64 q] fp32 staging
-  static constexpr int kVec = kDQ + kGDqTileBytes;       // lse*log2e, delta: [2][64] fp32
-  static constexpr int kBars = kVec + 2 * 64 * 4;
+  static constexpr int kVec = kDQ + kGDqTileBytes;       // lse*log2e, delta: 2 x [2][64] fp32
+  static constexpr int kBars = kVec + 2 * 2 * 64 * 4;
   static constexpr int kBytes = kBars + 256;
   static_assert(kBytes <= 232448, "shared memory budget of one CTA exceeded");
 };
@@ -75,6 +75,17 @@ __device__ __forceinline__ void bulk_wait_read0_g() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 __device__ __forceinline__ void bulk_wait0_g() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 
 // 16-byte chunk `c` (0..15) of staging / workspace row `row` (256 bytes = 64 fp32) sits at chunk
 // c ^ (row & 15): a warp writing one chunk of 32 consecutive rows then spreads over all banks.
@@ -235,7 +246,7 @@ flash_bwd_fused128_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
         ok = ok && issue_acc(i);
       }
     }
-  } else if (warp == 10) {
+  } else if (warp == 18) {
     // ------------------------------ dQ reducer ------------------------------
     if (elect_one()) {
       for (int i = 0; i < n_it; ++i) {
@@ -250,10 +261,10 @@ flash_bwd_fused128_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
     }
   } else {
     // ------------------------------ compute warps ------------------------------
-    const int cw = warp - 2;              // 0..7
+    const int cw = warp - 2;              // 0..15
     const int quad = warp % 4;            // TMEM lane quadrant of this warp
-    const int half = cw / 4;              // which 32 query columns of the 64
-    const int ct = cw * 32 + lane;        // 0..255 among the compute threads
+    const int cg = cw / 4;                // which 16 query columns of the 64
+    const int ct = cw * 32 + lane;        // 0..511 among the compute threads
     const int row = quad * 32 + lane;     // key within the tile (and head dim of dQ^T) = TMEM lane
     const int key = k0 + row;
     const uint32_t tlane = tmem + (static_cast<uint32_t>(quad * 32) << 16);
@@ -263,23 +274,30 @@ flash_bwd_fused128_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
     uint8_t* p_row = smem + L::kP + row * 128;
     uint8_t* ds_row = smem + L::kDS + row * 128;
     uint8_t* dq_row = smem + L::kDQ + row * 256;
-    float* v_lse = vec;
-    float* v_delta = vec + 64;
     bool ok = true;
+    // Per-column vectors (lse log2e and delta of the step's 64 queries): threads 0-127 fetch
+    // them one step ahead into a register and publish them through one of two shared-memory
+    // buffers, so that neither the global load nor a buffer hand-over sits in the step's chain.
+    auto fetch_vec = [&](int i) -> float {
+      const int qv = (first + i) * kGSub + (ct & 63);
+      if (ct >= 128 || i >= n_it || qv >= S) return ct < 64 ? INFINITY : 0.f;
+      return ct < 64 ? lse[vec_base + qv] * kGLog2e : delta[vec_base + qv];
+    };
+    float next_vec = fetch_vec(0);
 
     // dQ^T of step t: TMEM [128 dims][64 q] -> staging (rows swizzled), which the reducer sends
     // on. The caller has seen acc_done of step t.
     auto drain_dq = [&](int t) -> bool {
-      uint32_t o[32];
-      tmem_ld32(tlane + kColDQ + half * 32, o);
+      uint32_t o[16];
+      tmem_ld16(tlane + kColDQ + cg * 16, o);
       tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive(&bars->dq_drained);
       // the reduce of the previous step must have finished reading the staging buffer
       if (t > 0 && !mbar_wait(&bars->dq_sent, (t - 1) & 1, abort_flag)) return false;
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
-        *reinterpret_cast<uint4*>(dq_row + (dq_chunk(half * 8 + c, row) << 4)) =
+      for (int c = 0; c < 4; ++c)
+        *reinterpret_cast<uint4*>(dq_row + (dq_chunk(cg * 4 + c, row) << 4)) =
             make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
       fence_proxy_async_smem();
       mbar_arrive(&bars->dq_staged);
@@ -289,30 +307,28 @@ flash_bwd_fused128_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
     for (int i = 0; i < n_it; ++i) {
       const int q0 = (first + i) * kGSub;
       const bool diagonal = i < 2;   // sub-tiles that straddle the diagonal need the comparison
-      // per-column vectors of this query sub-tile (one buffer): w_full(i-1) complete = every
-      // compute thread is done with step i-1, reads of the vectors included
-      if (i > 0 && !(ok = mbar_wait(&bars->w_full, (i - 1) & 1, abort_flag))) break;
-      if (ct < 128) {
-        const int q = q0 + (ct & 63);
-        if (ct < 64) v_lse[ct] = q < S ? lse[vec_base + q] * kGLog2e : INFINITY;
-        else v_delta[ct - 64] = q < S ? delta[vec_base + q] : 0.f;
-      }
+      // Buffer i % 2 was last read in step i-2, and every thread finished that step before it
+      // arrived at vec_full(i-1), which this thread has already seen complete.
+      float* v_lse = vec + (i & 1) * 128;
+      float* v_delta = v_lse + 64;
+      if (ct < 128) v_lse[ct] = next_vec;   // threads 64-127 land in v_delta
+      next_vec = fetch_vec(i + 1);
       mbar_arrive(&bars->vec_full);
       if (!(ok = mbar_wait(&bars->vec_full, i & 1, abort_flag))) break;
       if (!(ok = mbar_wait(&bars->x_full, i & 1, abort_flag))) break;
       tc_fence_after_sync();
 
-      const int cbase = half * 32;
-      uint32_t x1[32], x2[32];
-      tmem_ld32(tlane + kColS + cbase, x1);
-      tmem_ld32(tlane + kColDP + cbase, x2);
+      const int cbase = cg * 16;
+      uint32_t x1[16], x2[16];
+      tmem_ld16(tlane + kColS + cbase, x1);
+      tmem_ld16(tlane + kColDP + cbase, x2);
       tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive(&bars->x_free);  // scores are in registers: the next step's GEMMs may overwrite
 
-      uint32_t pw[16], dw[16];
+      uint32_t pw[8], dw[8];
 #pragma unroll
-      for (int c = 0; c < 32; c += 4) {
+      for (int c = 0; c < 16; c += 4) {
         // 128-bit broadcast reads: all lanes of a warp want the same four columns
         const float4 a = *reinterpret_cast<const float4*>(v_lse + cbase + c);
         const float4 b = *reinterpret_cast<const float4*>(v_delta + cbase + c);
@@ -345,8 +361,8 @@ flash_bwd_fused128_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
         tc_fence_after_sync();
       }
 #pragma unroll
-      for (int v4 = 0; v4 < 4; ++v4) {
-        const int chunk = half * 4 + v4;  // 16-byte chunk within the 128-byte row
+      for (int v4 = 0; v4 < 2; ++v4) {
+        const int chunk = cg * 2 + v4;    // 16-byte chunk within the 128-byte row
         const int off = (chunk ^ (row & 7)) << 4;
         *reinterpret_cast<uint4*>(p_row + off) =
             make_uint4(pw[4 * v4], pw[4 * v4 + 1], pw[4 * v4 + 2], pw[4 * v4 + 3]);
@@ -358,17 +374,17 @@ flash_bwd_fused128_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
       if (i > 0 && !(ok = drain_dq(i - 1))) break;
     }
 
-    // the last step's dQ^T, then dV (half 0) and dK (half 1)
+    // the last step's dQ^T, then dV (column groups 0, 1) and dK (2, 3), 64 head dims each
     if (ok && (ok = mbar_wait(&bars->acc_done, (n_it - 1) & 1, abort_flag))) {
       tc_fence_after_sync();
       ok = drain_dq(n_it - 1);
     }
     if (ok) {
-      __nv_bfloat16* dst = (half == 0 ? dv : dk) + (vec_base + key) * D;
+      __nv_bfloat16* dst = (cg < 2 ? dv : dk) + (vec_base + key) * D + (cg & 1) * 64;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t o[32];
-        tmem_ld32(tlane + (half == 0 ? kColDV : kColDK) + c * 32, o);
+        tmem_ld32(tlane + (cg < 2 ? kColDV : kColDK) + (cg & 1) * 64 + c * 32, o);
         tmem_wait_ld();
         if (key < S) {
 #pragma unroll
