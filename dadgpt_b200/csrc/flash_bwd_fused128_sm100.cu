@@ -8,10 +8,13 @@
 //     p = exp2(S^T scale log2e - lse[q] log2e),  ds = p (dP^T - delta[q]) scale
 //     dV += P^T-tile dO      dK += dS^T-tile Q          accumulate in TMEM over the whole loop
 //     dQ^T-tile = K^T dS^T                              128 head dims x 64 queries, per step
-// P^T and dS^T are written once, bf16, [key][query] in the 128-byte swizzled layout: K-major A
-// operands of dV / dK, and the same dS^T bytes are the MN-major B operand of dQ^T, whose A
-// operand is the resident K tile read MN-major. Computing dQ transposed keeps all 128 TMEM
-// lanes busy (M = 128 head dims) although a step has only 64 queries.
+// P^T and dS^T go back into tensor memory as packed bf16 and are the A operands of dV / dK from
+// there (tcgen05.mma with A in TMEM): an MMA with both operands in shared memory reads them at
+// 128 B/clk, and with the TMA loads, the stores and the dQ staging the shared-memory traffic of
+// a step (336 KB when P^T / dS^T lived there), not the tensor core, set the step time. dS^T is
+// also written, bf16, [key][query] in the 128-byte swizzled layout, as the MN-major B operand
+// of dQ^T, whose A operand is the resident K tile read MN-major. Computing dQ transposed keeps
+// all 128 TMEM lanes busy (M = 128 head dims) although a step has only 64 queries.
 // Each step's dQ^T tile (32 KB fp32) goes TMEM -> staging in shared memory -> bulk reduce-add
 // into an fp32 workspace laid out tile by tile ([BH][64-query block][128 dims][64 queries], rows
 // swizzled as staged), which a last pass transposes and rounds to bf16. The sums into the
@@ -51,8 +54,7 @@ struct G128Smem {
   static constexpr int kQ = kV + kTile;
   static constexpr int kDO = kQ + kGStages * kSubTile;
   static constexpr int kDS = kDO + kGStages * kSubTile;  // [128 keys][64 q] bf16, one panel
-  static constexpr int kP = kDS + kGPanel;
-  static constexpr int kDQ = kP + kGPanel;               // [128 dims][64 q] fp32 staging
+  static constexpr int kDQ = kDS + kGPanel;              // [128 dims][64 q] fp32 staging
   static constexpr int kVec = kDQ + kGDqTileBytes;       // lse*log2e, delta: 2 x [2][64] fp32
   static constexpr int kBars = kVec + 2 * 2 * 64 * 4;
   static constexpr int kBytes = kBars + 256;
@@ -76,6 +78,12 @@ __device__ __forceinline__ void bulk_wait_read0_g() {
 }
 __device__ __forceinline__ void bulk_wait0_g() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%8], {%0, %1, %2, %3, %4, %5, %6, %7};"
+               ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                 "r"(taddr)
+               : "memory");
+}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -102,7 +110,10 @@ flash_bwd_fused128_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
   using L = G128Smem;
   constexpr int D = kGD;
   constexpr uint32_t kTmemCols = 512;
+  // S^T, dP^T (fp32, 64 columns each), dV, dK (128 each), dQ^T (64), then P^T and dS^T as packed
+  // bf16 (two queries per column: 32 columns each)
   constexpr uint32_t kColS = 0, kColDP = 64, kColDV = 128, kColDK = 256, kColDQ = 384;
+  constexpr uint32_t kColP = 448, kColDSt = 480;
 
   extern __shared__ __align__(1024) uint8_t smem[];
   G128Bars* bars = reinterpret_cast<G128Bars*>(smem + L::kBars);
@@ -187,7 +198,6 @@ flash_bwd_fused128_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
       const SmemDescBase v_kmaj = make_desc_base_sw128(smem_u32(smem + L::kV), 0);
       // K read as MN-major A (M = head dims): the two 64-dim panels are kGPanel apart
       const SmemDescBase k_mn = make_desc_base_sw128(smem_u32(smem + L::kK), kGPanel);
-      const SmemDescBase p_desc = make_desc_base_sw128(smem_u32(smem + L::kP), 0);
       const SmemDescBase ds_desc = make_desc_base_sw128(smem_u32(smem + L::kDS), 0);
       // streamed tiles: K-major B of the score GEMMs, MN-major B (panels kGSubPanel apart) of dV / dK
       const SmemDescBase q_desc0 = make_desc_base_sw128(smem_u32(smem + L::kQ), kGSubPanel);
@@ -222,8 +232,8 @@ flash_bwd_fused128_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
 #pragma unroll
         for (int kk = 0; kk < kGSub / 16; ++kk) {   // K dimension = 64 queries, 16 per MMA
           const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
-          mma_ss(tmem + kColDV, desc_at(p_desc, kk * 32), desc_at(dd, kk * 2048), idesc_a, acc);
-          mma_ss(tmem + kColDK, desc_at(ds_desc, kk * 32), desc_at(qd, kk * 2048), idesc_a, acc);
+          mma_ts(tmem + kColDV, tmem + kColP + kk * 8, desc_at(dd, kk * 2048), idesc_a, acc);
+          mma_ts(tmem + kColDK, tmem + kColDSt + kk * 8, desc_at(qd, kk * 2048), idesc_a, acc);
         }
         // the previous step's dQ^T must have left tensor memory before this one overwrites it;
         // the compute warps read it right after they publish P^T / dS^T, while dV / dK are running
@@ -271,7 +281,6 @@ flash_bwd_fused128_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
     const float scale_log2 = scale * kGLog2e;
     const float keep_scale = DROP ? 1.0f / (1.0f - rate) : 1.0f;
     const size_t vec_base = static_cast<size_t>(bh) * S;
-    uint8_t* p_row = smem + L::kP + row * 128;
     uint8_t* ds_row = smem + L::kDS + row * 128;
     uint8_t* dq_row = smem + L::kDQ + row * 256;
     bool ok = true;
@@ -360,15 +369,18 @@ flash_bwd_fused128_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
         if (!(ok = mbar_wait(&bars->acc_done, (i - 1) & 1, abort_flag))) break;
         tc_fence_after_sync();
       }
+      // sixteen queries = eight packed columns = one K step of the dV / dK MMAs
+      tmem_st8(tlane + kColP + cg * 8, pw);
+      tmem_st8(tlane + kColDSt + cg * 8, dw);
 #pragma unroll
       for (int v4 = 0; v4 < 2; ++v4) {
         const int chunk = cg * 2 + v4;    // 16-byte chunk within the 128-byte row
         const int off = (chunk ^ (row & 7)) << 4;
-        *reinterpret_cast<uint4*>(p_row + off) =
-            make_uint4(pw[4 * v4], pw[4 * v4 + 1], pw[4 * v4 + 2], pw[4 * v4 + 3]);
         *reinterpret_cast<uint4*>(ds_row + off) =
             make_uint4(dw[4 * v4], dw[4 * v4 + 1], dw[4 * v4 + 2], dw[4 * v4 + 3]);
       }
+      tmem_wait_st();
+      tc_fence_before_sync();
       fence_proxy_async_smem();
       mbar_arrive(&bars->w_full);
       if (i > 0 && !(ok = drain_dq(i - 1))) break;
