@@ -38,6 +38,7 @@ namespace {
 constexpr int kDecodeWarps = 8;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
 constexpr int kDecodeBatch = 4;   // row groups whose loads a lane keeps in flight
+constexpr unsigned kTicketGroups = 32;  // first-level counters of the "all lengths read" tickets
 constexpr int kMinChunk = 256;    // smallest number of cache rows a CTA is given
 constexpr int kTargetCtas = 592;  // 4 per SM: below that the cache is split across CTAs
 
@@ -92,22 +93,22 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
   return r;
 }
 
-// Workspace: one ticket per (sequence, head) and one per sequence (uint32, zero between calls),
-// padded to 256 bytes, then the records [B*H][splits][D + 2] fp32 (unnormalised output, max, sum).
+// Workspace: one ticket per (sequence, head), then the 1 + kTicketGroups counters of the "all
+// lengths read" tickets (uint32, zero between calls), padded to 256 bytes, then the records [B*H][splits][D + 2] fp32 (unnormalised output, max, sum).
 __host__ __device__ inline size_t partial_stride(int D) { return static_cast<size_t>(D) + 2; }
 inline size_t record_bytes(int B, int H, int D, int max_len) {
   const int splits = split_count(B, H, max_len);
   return static_cast<size_t>(B) * H * splits * partial_stride(D) * sizeof(float);
 }
 inline size_t ticket_bytes(int B, int H) {
-  return (sizeof(uint32_t) * (static_cast<size_t>(B) * H + B) + 255) / 256 * 256;
+  return (sizeof(uint32_t) * (static_cast<size_t>(B) * H + 1 + kTicketGroups) + 255) / 256 * 256;
 }
 inline size_t workspace_bytes(int B, int H, int D, int max_len) {
   return ticket_bytes(B, H) + (record_bytes(B, H, D, max_len) + 255) / 256 * 256;
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kDecodeThreads)
+__global__ void __launch_bounds__(kDecodeThreads, 3)
 decode_splitk_kernel(T* __restrict__ out, float* __restrict__ partial,
                      unsigned* __restrict__ tickets, unsigned* __restrict__ seq_tickets,
                      const T* __restrict__ q, const T* __restrict__ k_new,
@@ -124,7 +125,7 @@ decode_splitk_kernel(T* __restrict__ out, float* __restrict__ partial,
   pdl_launch_dependents();
 
   const int split = blockIdx.y, splits = gridDim.y;
-  __shared__ int sh_len, sh_b, sh_last;
+  __shared__ int sh_len, sh_b, sh_last, sh_adv;
   __shared__ __align__(16) int sh_lens[kDecodeThreads];
   __shared__ int sh_rank[kDecodeThreads];
   __shared__ float sh_acc[kDecodeWarps][D];
@@ -172,16 +173,49 @@ decode_splitk_kernel(T* __restrict__ out, float* __restrict__ partial,
     sh_len = lengths ? lengths[slot_seq] : fixed_len;  // rows already in the cache
   }
   __syncthreads();  // the CTA's ticket below is taken strictly after these reads
+  // Every CTA of the call draws a ticket once it has read the lengths (all of them, when it
+  // ranks the sequences); whoever holds the last one knows that nobody will read them again and
+  // advances them. Two levels keep the atomics off one address: the CTAs are dealt into
+  // kTicketGroups groups, a CTA draws its group's ticket here, at the start, and looks at it
+  // only at the very end (the round trip through L2 costs it nothing); the last of each group
+  // then draws from a second counter, and the last of those advances the lengths.
+  unsigned my_ticket = 0;
+  if (lengths != nullptr && threadIdx.x == 0)
+    my_ticket = atomicAdd(&seq_tickets[1 + (blockIdx.y * gridDim.x + blockIdx.x) % kTicketGroups], 1u);
+  auto advance_lengths = [&]() {
+    if (lengths == nullptr) return;
+    if (threadIdx.x == 0) {
+      // recomputed here rather than kept in registers across the main loop: the kernel lives on
+      // three CTAs per SM
+      const unsigned all_ctas = gridDim.x * gridDim.y;
+      const unsigned group = (blockIdx.y * gridDim.x + blockIdx.x) % kTicketGroups;
+      const unsigned group_size = (all_ctas - group + kTicketGroups - 1) / kTicketGroups;
+      int last = 0;
+      if (my_ticket == group_size - 1) {
+        seq_tickets[1 + group] = 0;   // ready for the next call
+        const unsigned groups = all_ctas < kTicketGroups ? all_ctas : kTicketGroups;
+        last = atomicAdd(&seq_tickets[0], 1u) == groups - 1;
+        if (last) seq_tickets[0] = 0;
+      }
+      sh_adv = last;
+    }
+    __syncthreads();
+    if (!sh_adv) return;
+    for (int s = threadIdx.x; s < n_seq; s += kDecodeThreads) {
+      const int l = lengths[s];
+      if (l >= 0 && l < max_len) lengths[s] = l + 1;   // a full or invalid sequence is left alone
+    }
+  };
   const int b = sh_b;
   const int bh = b * H + static_cast<int>(blockIdx.x) % H;
   const int len = sh_len;
   if (len < 0 || len >= max_len) {
     if (split == 0 && bh % H == 0 && threadIdx.x == 0) atomicExch(status, DADATTN_E_ARG);
+    advance_lengths();
     return;
   }
   const int total = len + 1;  // rows visible to the new token, itself included
   const int n_active = (total + chunk - 1) / chunk;
-  const bool direct = lengths == nullptr;
 
   if (split < n_active) {
     const int row_begin = split * chunk;
@@ -326,15 +360,7 @@ decode_splitk_kernel(T* __restrict__ out, float* __restrict__ partial,
     }
   }
 
-  // Every CTA of the sequence has read its length by the time it takes this ticket; the last
-  // one may therefore advance it.
-  if (!direct && threadIdx.x == 0) {
-    const unsigned all = static_cast<unsigned>(H) * splits;
-    if (atomicAdd(&seq_tickets[b], 1u) == all - 1) {
-      seq_tickets[b] = 0;
-      lengths[b] = len + 1;
-    }
-  }
+  advance_lengths();
 }
 
 template <int DH>

@@ -198,7 +198,7 @@ int dadattn_decode_bf16(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
  * workspace: the split-K partials go to a fixed 8 MiB array inside the library image (held by
  * every GPU that loads the library, until exit). The call performs no cudaMalloc/cudaFree and
  * uses no allocating routine.
- *  - Limit: the array is 8 MiB (8388608 bytes): 64 KiB of split-K tickets (B*H + B <= 16384)
+ *  - Limit: the array is 8 MiB (8388608 bytes): 64 KiB of tickets (B*H + 33 <= 16384)
  *    and the rest for records (none when B*H >= 592, where each CTA walks a whole sequence);
  *    dadattn_decode_workspace_bytes(B,H,D,max_len) tells what a shape needs, and shapes that
  *    need more than the array holds return DADATTN_E_WORKSPACE.
