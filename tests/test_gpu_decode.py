@@ -84,6 +84,33 @@ def test_batched_bf16_decode_against_oracle(cuda, oracle, D):
     assert device_status() == 0
 
 
+def test_many_sequences_with_tied_lengths_are_each_attended_once(cuda, oracle):
+    """Enough (sequence, head) pairs that the CTAs no longer fit the GPU at once: the kernel then
+    takes the sequences longest first, ranking the lengths itself. Tied and adjacent lengths are
+    the hard case for that ranking (every CTA must arrive at the same order, also while other
+    CTAs finish); every pair must still be attended exactly once, over several steps."""
+    B, H, L, D = 48, 12, 160, 64
+    cache = dad.KVCacheBF16(B, H, L, D, device=cuda)
+    cache.k.copy_(torch.randn(B, H, L, D, device=cuda))
+    cache.v.copy_(torch.randn(B, H, L, D, device=cuda))
+    g = torch.Generator().manual_seed(11)
+    lens = torch.randint(100, 104, (B,), generator=g, dtype=torch.int32)
+    lens[::7] = 30
+    cache.lengths.copy_(lens.to(cuda))
+    scale = D ** -0.5
+    for step in range(3):
+        q, kn, vn = (torch.randn(B, H, D, device=cuda).to(torch.bfloat16) for _ in range(3))
+        out = torch.full_like(q, float("nan"))
+        before = cache.lengths.clone()
+        dad.decode_attention_bf16(out, q, kn, vn, cache, scale)
+        torch.cuda.synchronize()
+        assert torch.equal(cache.lengths, before + 1)
+        want = oracle.decode(q.float().cpu().numpy(), cache.k.float().cpu().numpy(),
+                             cache.v.float().cpu().numpy(), cache.lengths.cpu().numpy(), scale)
+        assert max_abs(out.float().cpu().numpy(), want) <= 2e-2
+    assert device_status() == 0
+
+
 def test_full_sequence_is_skipped_and_reported(cuda):
     B, H, L, D = 2, 2, 16, 64
     cache = dad.KVCacheBF16(B, H, L, D, device=cuda)
