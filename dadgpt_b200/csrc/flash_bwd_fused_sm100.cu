@@ -52,13 +52,15 @@ struct FusedSmem {
   static constexpr int kDS = kP + 2 * kFPanel;
   static constexpr int kDQ = kDS + 2 * kFPanel;         // [128 q][64] fp32, two 128-byte panels
   static constexpr int kBars = kDQ + 2 * kFPanel;
-  static constexpr int kBytes = kBars + 256;
+  static constexpr int kVec = kBars + 256;              // 2 x [lse log2e | delta][128] fp32
+  static constexpr int kBytes = kVec + 2 * 2 * 128 * 4;
+  static_assert(kBytes <= 232448, "shared memory budget of one CTA exceeded");
 };
 
 struct FusedBars {
   uint64_t kv_full[2], dkv_sent[2], q_full[kFStages], do_full[kFStages], qdo_empty[kFStages];
   uint64_t item_ready[kFRing], item_free[kFRing];
-  uint64_t x_full, x_free, w_full, acc_done, dq_drained, dq_staged, dq_sent, dkv_staged;
+  uint64_t x_full, x_free, w_full, acc_done, dq_drained, dq_staged, dq_sent, dkv_staged, vec_full[2];
   int ring[kFRing];
   uint32_t tmem_base;
   int abort_flag;
@@ -186,6 +188,8 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     mbar_init(&bars->dq_staged, kFCompute);
     mbar_init(&bars->dq_sent, 1);
     mbar_init(&bars->dkv_staged, kFCompute);
+    mbar_init(&bars->vec_full[0], 128);
+    mbar_init(&bars->vec_full[1], 128);
     bars->abort_flag = 0;
     fence_mbar_init();
   }
@@ -441,10 +445,15 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       fence_proxy_async_smem();
       mbar_arrive(&bars->dkv_staged);
     };
-    // per-row scalars, fetched one tile ahead: their loads share the SM's path to L2 with the dQ
-    // reduce traffic and would otherwise stall the arithmetic. Queries beyond S contribute
-    // nothing (p = exp2(-inf) = 0).
+    // Per-row scalars (lse log2e and delta of the tile's 128 queries). The four threads that
+    // share a row need the same two values; only the first of them (column group 0: 128 threads)
+    // loads them, one tile ahead, and hands them over through one of two shared-memory buffers:
+    // global loads of the compute warps queue behind the dQ reduce traffic on the SM's path to
+    // L2, so there should be few of them and none whose latency is exposed. Queries beyond S
+    // contribute nothing (p = exp2(-inf) = 0).
+    float* vec = reinterpret_cast<float*>(smem + L::kVec);
     auto load_row = [&](bool valid, int q_tile, int bh, float& l2, float& dl) {
+      if (cg != 0) return;
       const int qq = q_tile * kFT + row;
       const bool in = valid && qq < S;
       const size_t at = static_cast<size_t>(bh) * S + qq;
@@ -469,7 +478,14 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int q = (t.kt + i) * kFT + row;
         const bool diagonal = (i == 0);
         const bool new_item = (i == 0 && j > 0);  // the item before this one is complete
-        const float row_lse2 = next_lse2, row_delta_s = next_delta * scale;
+        // Buffer g % 2 was last read in tile g-2, which every thread had finished before the
+        // accumulating GEMMs of tile g-2 could complete, and this thread has seen them complete.
+        float* vbuf = vec + (g & 1) * 256;
+        if (cg == 0) {
+          vbuf[row] = next_lse2;
+          vbuf[128 + row] = next_delta * scale;
+          mbar_arrive(&bars->vec_full[g & 1]);
+        }
         if (i + 1 < t.n_it) {
           load_row(true, t.kt + i + 1, t.bh, next_lse2, next_delta);
         } else {
@@ -477,6 +493,10 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           load_row(nxt < n_items, tn.kt, tn.bh, next_lse2, next_delta);
         }
         if (warp == 2) DAD_TRACE(0);
+        // (one barrier per buffer: the next completion of this one needs the GEMMs of tile g,
+        // hence this thread's own P / dS, so its phase cannot run away from a slow waiter)
+        if (!(ok = mbar_wait(&bars->vec_full[g & 1], (g >> 1) & 1, abort_flag))) break;
+        const float row_lse2 = vbuf[row], row_delta_s = vbuf[128 + row];
         if (!(ok = mbar_wait(&bars->x_full, g & 1, abort_flag))) break;
         if (warp == 2) DAD_TRACE(0);
         tc_fence_after_sync();
