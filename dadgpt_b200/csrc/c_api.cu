@@ -23,8 +23,9 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 
-// One 4-byte word per device, allocated the first time a kernel that can report a condition is
-// launched on that device (the only allocation the library makes; it lives until exit).
+// Two 4-byte words per device (status, and a detail for it: the source line of a wait that ran
+// out), allocated the first time a kernel that can report a condition is launched on that
+// device; they live until exit.
 int* device_status_word() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
@@ -34,7 +35,7 @@ int* device_status_word() {
   std::lock_guard<std::mutex> lock(g_status_mutex);
   if (!g_status[dev]) {
     int* p = nullptr;
-    if (cudaMalloc(&p, sizeof(int)) != cudaSuccess || cudaMemset(p, 0, sizeof(int)) != cudaSuccess) {
+    if (cudaMalloc(&p, 2 * sizeof(int)) != cudaSuccess || cudaMemset(p, 0, 2 * sizeof(int)) != cudaSuccess) {
       fail(DADATTN_E_CUDA, "cannot allocate the device status word: %s",
            cudaGetErrorString(cudaGetLastError()));
       return nullptr;
@@ -55,14 +56,16 @@ extern "C" const char* dadattn_version(void) { return "dadattn 0.1 sm_100a"; }
 extern "C" int dadattn_device_status(dadattn_stream_t stream) {
   int* word = device_status_word();
   if (!word) return DADATTN_E_CUDA;
-  int host = 0;
+  int host[2] = {0, 0};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  DAD_CUDA(cudaMemcpyAsync(&host, word, sizeof(int), cudaMemcpyDeviceToHost, st));
-  DAD_CUDA(cudaMemsetAsync(word, 0, sizeof(int), st));
+  DAD_CUDA(cudaMemcpyAsync(host, word, 2 * sizeof(int), cudaMemcpyDeviceToHost, st));
+  DAD_CUDA(cudaMemsetAsync(word, 0, 2 * sizeof(int), st));
   DAD_CUDA(cudaStreamSynchronize(st));
-  if (host == DADATTN_E_TIMEOUT) fail(host, "a bounded device-side wait ran out");
-  else if (host == DADATTN_E_ARG) fail(host, "a kernel skipped work: sequence length outside [0, max_len)");
-  else if (host != 0) fail(host, "device status %d", host);
-  return host;
+  if (host[0] == DADATTN_E_TIMEOUT)
+    fail(host[0], "a bounded device-side wait ran out (wait at source line %d of its kernel)", host[1]);
+  else if (host[0] == DADATTN_E_ARG)
+    fail(host[0], "a kernel skipped work: sequence length outside [0, max_len)");
+  else if (host[0] != 0)
+    fail(host[0], "device status %d", host[0]);
+  return host[0];
 }
-

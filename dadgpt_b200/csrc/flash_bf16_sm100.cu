@@ -472,7 +472,7 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
     tc_fence_after_sync();
     tmem_dealloc(tmem, kTmemCols);
   }
-  if (threadIdx.x == 0 && bars->abort_flag) atomicExch(status, DADATTN_E_TIMEOUT);
+  if (threadIdx.x == 0 && bars->abort_flag) report_timeout(status, bars->abort_flag);
 }
 
 template <int D, bool DROP>

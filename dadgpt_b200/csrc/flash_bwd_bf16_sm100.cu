@@ -408,7 +408,7 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
     tc_fence_after_sync();
     tmem_dealloc(tmem, kTmemCols);
   }
-  if (threadIdx.x == 0 && bars->abort_flag) atomicExch(status, DADATTN_E_TIMEOUT);
+  if (threadIdx.x == 0 && bars->abort_flag) report_timeout(status, bars->abort_flag);
 }
 
 template <int D, bool DROP>

@@ -596,7 +596,7 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     tc_fence_after_sync();
     tmem_dealloc(tmem, kTmemCols);
   }
-  if (threadIdx.x == 0 && bars->abort_flag) atomicExch(status, DADATTN_E_TIMEOUT);
+  if (threadIdx.x == 0 && bars->abort_flag) report_timeout(status, bars->abort_flag);
 }
 
 // delta[r] = sum_d dO[r,d] O[r,d] (reference flash_delta_kernel, cuda/attention.cu:76-85) and the

@@ -54,12 +54,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-constexpr uint32_t kSpinLimit = 1u << 22;  // with the back-off below: a few tenths of a second
+constexpr uint32_t kSpinLimit = 1u << 24;  // with the back-off below: a few seconds
 
 // Waits for the phase with the given parity to complete. `abort_flag` (shared memory) is
-// polled too: once any thread of the CTA has given up, everybody leaves quickly.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
-                                          volatile int* abort_flag) {
+// polled too: once any thread of the CTA has given up, everybody leaves quickly. The thread
+// whose own wait runs out leaves `site` (the source line of the wait, through DAD_MBAR_WAIT)
+// in the flag, from where the kernel's exit path copies it next to the device status word.
+__device__ __forceinline__ bool mbar_wait_at(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                             int site) {
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 32) {
@@ -67,8 +69,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
       __nanosleep(i > 4096 ? 256 : 32);
     }
   }
-  *abort_flag = 1;
+  atomicCAS(const_cast<int*>(abort_flag), 0, site);
   return false;
+}
+#define mbar_wait(bar, parity, abort_flag) mbar_wait_at(bar, parity, abort_flag, __LINE__)
+
+// Common exit of a kernel whose CTA raised its abort flag: the flag holds the line of the wait
+// that ran out; it goes to the word behind the status word, the status becomes E_TIMEOUT.
+__device__ __forceinline__ void report_timeout(int* status, int site) {
+  status[1] = site;
+  atomicExch(status, DADATTN_E_TIMEOUT);
 }
 
 // ---- proxies / fences -----------------------------------------------------------------------

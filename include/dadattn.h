@@ -217,7 +217,8 @@ int dadattn_decode_bf16_noalloc(uint16_t* out, const uint16_t* q, const uint16_t
 
 /* Synchronises the stream and returns the sticky device-side status word of this device
  * (0, or a DADATTN_E_* code recorded by a kernel: a bounded wait that ran out, a sequence at
- * max_len). Clears the word. */
+ * max_len). Clears the word. For a wait that ran out dadattn_last_error() names the source line
+ * of that wait inside its kernel. */
 int dadattn_device_status(dadattn_stream_t stream);
 
 #ifdef __cplusplus
