@@ -336,8 +336,13 @@ def run_ours(args):
         status = device_status()
         if max_over_ranks(float(status != 0)) == 0.0:
             break
-        if status != 0:
-            problems.append(_lib.load().dadattn_last_error().decode(errors="replace"))
+        mine = (f"rank {rank}: " + _lib.load().dadattn_last_error().decode(errors="replace")) if status != 0 else None
+        if world > 1:
+            everyone = [None] * world
+            dist.all_gather_object(everyone, mine)
+        else:
+            everyone = [mine]
+        problems.extend(x for x in everyone if x)
         if retries == 2:
             raise RuntimeError(f"device status {status} after the timed region: {problems}")
         retries += 1
