@@ -60,7 +60,7 @@ struct FusedSmem {
 struct FusedBars {
   uint64_t kv_full[2], dkv_sent[2], q_full[kFStages], do_full[kFStages], qdo_empty[kFStages];
   uint64_t item_ready[kFRing], item_free[kFRing];
-  uint64_t x_full, x_free, w_full, acc_done, dq_drained, dq_staged, dq_sent, dkv_staged, vec_full[2];
+  uint64_t x_full, x_free, w_full, acc_done, dq_drained, dq_staged, dq_sent, dkv_staged[2], vec_full[2];
   int ring[kFRing];
   uint32_t tmem_base;
   int abort_flag;
@@ -187,7 +187,8 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     mbar_init(&bars->dq_drained, kFCompute);
     mbar_init(&bars->dq_staged, kFCompute);
     mbar_init(&bars->dq_sent, 1);
-    mbar_init(&bars->dkv_staged, kFCompute);
+    mbar_init(&bars->dkv_staged[0], kFCompute);
+    mbar_init(&bars->dkv_staged[1], kFCompute);
     mbar_init(&bars->vec_full[0], 128);
     mbar_init(&bars->vec_full[1], 128);
     bars->abort_flag = 0;
@@ -371,7 +372,13 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // The item's dK / dV were staged (in its K / V buffers) before the dQ of its last
             // tile. Their stores go behind the reduce, so that the dQ staging buffer is handed
             // back as soon as the reduce has read it; the K / V buffers follow.
-            if (!(ok = mbar_wait(&bars->dkv_staged, j & 1, abort_flag))) break;
+            // One barrier per K / V buffer, not one for all items: after a single-tile item the
+            // compute warps stage the next item's dK / dV without needing this warp, so a single
+            // barrier could run two phases ahead of a late reducer, whose parity wait would then
+            // never be satisfied (and the compute warps in turn wait for this warp's dq_sent).
+            // The next phase of dkv_staged[j & 1] belongs to item j + 2 and cannot complete
+            // before this warp has handed back the staging buffer of item j's last tile.
+            if (!(ok = mbar_wait(&bars->dkv_staged[j & 1], (j >> 1) & 1, abort_flag))) break;
             tma_store_3d(&map_dk, smem + L::kK + (j & 1) * kFPanel, 0, t.kt * kFT, t.bh);
             tma_store_3d(&map_dv, smem + L::kV + (j & 1) * kFPanel, 0, t.kt * kFT, t.bh);
             bulk_commit();
@@ -443,7 +450,7 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       tc_fence_before_sync();
       fence_proxy_async_smem();
-      mbar_arrive(&bars->dkv_staged);
+      mbar_arrive(&bars->dkv_staged[kb]);
     };
     // Per-row scalars (lse log2e and delta of the tile's 128 queries). The four threads that
     // share a row need the same two values; only the first of them (column group 0: 128 threads)
