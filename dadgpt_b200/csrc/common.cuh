@@ -78,32 +78,6 @@ __device__ __forceinline__ bool philox_keep(const PhiloxKey& p, uint64_t subsequ
   return !(u < rate);
 }
 
-// Optional phase tracing (compile with -DDADATTN_TRACE; never in the shipped build): lane 0 of a
-// role in CTA (0,0) appends clock64() stamps to a device buffer that dadattn_trace_read copies out.
-#ifdef DADATTN_TRACE
-constexpr int kTraceRoles = 4, kTraceSlots = 2048;
-static __device__ long long g_trace[kTraceRoles][kTraceSlots];  // one copy per translation unit
-// Defines extern "C" int NAME(long long* host) that copies this translation unit's stamps out.
-#define DAD_TRACE_READER(NAME)                                                              \
-  extern "C" int NAME(long long* host) {                                                   \
-    if (cudaDeviceSynchronize() != cudaSuccess) return DADATTN_E_CUDA;                      \
-    return cudaMemcpyFromSymbol(host, ::dadattn::g_trace,                                   \
-                                sizeof(long long) * ::dadattn::kTraceRoles *               \
-                                    ::dadattn::kTraceSlots) == cudaSuccess                  \
-               ? DADATTN_OK                                                                 \
-               : DADATTN_E_CUDA;                                                            \
-  }
-#define DAD_TRACE_DECL int trace_n_ = 0; const bool trace_on_ = (blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x % 32) == 0)
-#define DAD_TRACE(role)                                                          \
-  do {                                                                           \
-    if (trace_on_ && trace_n_ < ::dadattn::kTraceSlots) ::dadattn::g_trace[role][trace_n_++] = clock64(); \
-  } while (0)
-#else
-#define DAD_TRACE_DECL
-#define DAD_TRACE(role)
-#define DAD_TRACE_READER(NAME)
-#endif
-
 // Launch with programmatic stream serialization: the grid may become resident while its
 // predecessor in the stream drains, runs its set-up (barriers, TMEM, descriptor prefetch), and
 // parks in pdl_wait() until the predecessor has completed and flushed its memory. Kernels

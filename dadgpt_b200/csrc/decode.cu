@@ -98,6 +98,7 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
 __host__ __device__ inline size_t partial_stride(int D) { return static_cast<size_t>(D) + 2; }
 inline size_t record_bytes(int B, int H, int D, int max_len) {
   const int splits = split_count(B, H, max_len);
+  if (splits == 1) return 0;  // every CTA finishes its (sequence, head) itself: no records
   return static_cast<size_t>(B) * H * splits * partial_stride(D) * sizeof(float);
 }
 inline size_t ticket_bytes(int B, int H) {
@@ -487,6 +488,8 @@ extern "C" int dadattn_decode_f32(float* out, const float* q, const float* k_new
 // 64 KiB are the tickets, at a fixed place whatever the shape of a call: they are zero when the
 // module is loaded and every call returns them to zero, which is the only state a call needs
 // from its predecessors. The records behind them are written before they are read.
+// A sequence that is already at max_len is skipped and noted in g_decode_noalloc_status, which
+// dadattn_decode_noalloc_status() reads and clears (a symbol copy: no allocation either).
 // ---------------------------------------------------------------------------------------------
 namespace dadattn {
 namespace {
@@ -531,13 +534,15 @@ extern "C" int dadattn_decode_bf16_noalloc(uint16_t* out, const uint16_t* q,
                                            dadattn_stream_t stream) {
   if (int rc = check_decode_bf16(out, q, k_new, v_new, k_cache, v_cache, lengths, B, H, D, max_len))
     return rc;
-  const size_t need = dadattn_decode_workspace_bytes(B, H, D, max_len);
-  if (need > kNoAllocScratchBytes || ticket_bytes(B, H) > kNoAllocTicketBytes ||
-      record_bytes(B, H, D, max_len) > kNoAllocScratchBytes - kNoAllocTicketBytes)
+  const size_t need_tickets = ticket_bytes(B, H), need_records = record_bytes(B, H, D, max_len);
+  if (need_tickets > kNoAllocTicketBytes || need_records > kNoAllocScratchBytes - kNoAllocTicketBytes)
     return fail(DADATTN_E_WORKSPACE,
-                "decode (no-alloc): B=%d H=%d D=%d max_len=%d needs %zu bytes of split-K scratch, "
-                "the built-in array holds %zu; use dadattn_decode_bf16 with your own workspace",
-                B, H, D, max_len, need, static_cast<size_t>(kNoAllocScratchBytes));
+                "decode (no-alloc): B=%d H=%d D=%d max_len=%d needs %zu bytes of tickets and %zu "
+                "bytes of split-K records; the built-in array of %zu bytes holds %zu and %zu; use "
+                "dadattn_decode_bf16 with your own workspace",
+                B, H, D, max_len, need_tickets, need_records,
+                static_cast<size_t>(kNoAllocScratchBytes), static_cast<size_t>(kNoAllocTicketBytes),
+                static_cast<size_t>(kNoAllocScratchBytes - kNoAllocTicketBytes));
   float* scratch = nullptr;
   int* status = nullptr;
   if (int rc = noalloc_setup(&scratch, &status)) return rc;
@@ -548,4 +553,20 @@ extern "C" int dadattn_decode_bf16_noalloc(uint16_t* out, const uint16_t* q,
                                           max_len, scale, tickets, partial, status, st)
                  : launch_decode_bf16<128>(out, q, k_new, v_new, k_cache, v_cache, lengths, B, H,
                                            max_len, scale, tickets, partial, status, st);
+}
+
+extern "C" int dadattn_decode_noalloc_status(dadattn_stream_t stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int host = 0;
+  const int zero = 0;
+  DAD_CUDA(cudaMemcpyFromSymbolAsync(&host, g_decode_noalloc_status, sizeof(int), 0,
+                                     cudaMemcpyDeviceToHost, st));
+  DAD_CUDA(cudaMemcpyToSymbolAsync(g_decode_noalloc_status, &zero, sizeof(int), 0,
+                                   cudaMemcpyHostToDevice, st));
+  DAD_CUDA(cudaStreamSynchronize(st));
+  if (host == DADATTN_E_ARG)
+    fail(host, "decode (no-alloc): a sequence was skipped, its length is outside [0, max_len)");
+  else if (host != 0)
+    fail(host, "decode (no-alloc): device status %d", host);
+  return host;
 }

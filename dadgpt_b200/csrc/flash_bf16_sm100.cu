@@ -111,15 +111,17 @@ struct FwdBars {
 };
 
 // 2^x on the FMA pipe: integer part through the float-rounding trick, fractional part in
-// [-0.5, 0.5] through a cubic (relative error 6e-4, below bf16's half ulp of 2e-3).
-__device__ __forceinline__ float ex2_poly(float x) {
-  x = fmaxf(x, -125.f);
+// [-0.5, 0.5] through a cubic (relative error 6e-4, below bf16's half ulp of 2e-3). Arguments
+// below -125 (masked scores are -inf) give exactly 0, as ex2.approx.ftz does.
+__device__ __forceinline__ float ex2_poly(float x0) {
+  const float x = fmaxf(x0, -125.f);
   const float t = x + 12582912.f;   // 1.5 * 2^23: the integer part lands in the low mantissa bits
   const float f = x - (t - 12582912.f);
   float p = fmaf(f, 0.0555041087f, 0.2402265070f);
   p = fmaf(p, f, 0.6931471806f);
   p = fmaf(p, f, 1.0f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+  const float r = __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+  return x0 < -125.f ? 0.f : r;
 }
 
 template <int D, bool DROP>
@@ -143,10 +145,6 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-#ifdef DADATTN_TRACE
-  int life_n_ = 0;
-  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_trace[3][life_n_++] = clock64();
-#endif
   const int qt = gridDim.x - 1 - blockIdx.x;  // heaviest tiles first
   const int bh = blockIdx.y;
   const int q0 = qt * kBM;
@@ -188,9 +186,6 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
   // may have produced. Once every CTA of this grid is here the next grid may start its set-up.
   pdl_wait();
   pdl_launch_dependents();
-#ifdef DADATTN_TRACE
-  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_trace[3][life_n_++] = clock64();
-#endif
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -227,14 +222,12 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
       const SmemDescBase v_desc0 = make_desc_base_sw128(smem_u32(smem + L::kV), kPanelBytes);
       constexpr uint32_t kStageBytes = kPanels * kPanelBytes;
       bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
-      DAD_TRACE_DECL;
 
       // O_h[:, 64 pn .. 64 pn + 63] (+)= P_i[:, 64 h .. 64 h + 63] V_i[64 h .. 64 h + 63, :]
       auto issue_pv = [&](int i) -> bool {
         const int s = i % kStages;
         if (!mbar_wait(&bars->v_full[s], (i / kStages) & 1, abort_flag)) return false;
         if (!mbar_wait(&bars->p_full, i & 1, abort_flag)) return false;
-        DAD_TRACE(1);
         tc_fence_after_sync();
         const SmemDescBase v_desc{v_desc0.lo + s * (kStageBytes >> 4), v_desc0.hi};
         // One MMA per 16 keys covers all D output columns: the V tile is MN-major, its 64-column
@@ -253,7 +246,6 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         mma_commit(&bars->v_empty[s]);
         mma_commit(&bars->o_done[i & 1]);
-        DAD_TRACE(1);
         return true;
       };
 
@@ -268,7 +260,6 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
         if (!L::kPTmem && ok && j >= kSBufs)
           ok = mbar_wait(&bars->s_free[sb], (j / kSBufs - 1) & 1, abort_flag);
         if (!ok) break;
-        DAD_TRACE(1);
         tc_fence_after_sync();
         const SmemDescBase k_desc{k_desc0.lo + s * (kStageBytes >> 4), k_desc0.hi};
 #pragma unroll
@@ -279,7 +270,6 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         mma_commit(&bars->k_empty[s]);
         mma_commit(&bars->s_full[sb]);
-        DAD_TRACE(1);
         if (!(L::kPTmem && kSBufs == 1) && j > 0) ok = issue_pv(j - 1);
       }
       if (ok) issue_pv(n_kv - 1);
@@ -299,13 +289,11 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
     auto wait_pv = [&](int i) { return mbar_wait(&bars->o_done[i & 1], (i >> 1) & 1, abort_flag); };
     float m = -INFINITY, l = 0.f;  // running max (log2 units, scaled) and sum of this half-row
     bool ok = true;
-    DAD_TRACE_DECL;
 
     for (int j = 0; j < n_kv; ++j) {
       const int sb = j % kSBufs;
       const uint32_t tS = tlane + kColS + sb * 128 + half * 64;
       if (!(ok = mbar_wait(&bars->s_full[sb], (j / kSBufs) & 1, abort_flag))) break;
-      if (warp == 2) DAD_TRACE(0);
       tc_fence_after_sync();
       const int c0 = j * kBN + half * 64;  // first key of this thread's 64 columns
       // Only the diagonal tile needs the causal mask: columns beyond `limit` are dropped.
@@ -344,7 +332,6 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
       for (int i = 0; i < 32; ++i)
         mx4[i & 3] = fmaxf(mx4[i & 3], fmaxf(__uint_as_float(xa[i]), __uint_as_float(xb[i])));
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
-      if (warp == 2) DAD_TRACE(0);
 
       bool waited_o = false;
       if (j == 0) {
@@ -372,7 +359,6 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
       // P in shared memory: the MMA that read the buffer last (tile j - 1) must have completed
       if (!L::kPTmem && j > 0 && !waited_o && !(ok = wait_pv(j - 1))) break;
       uint8_t* p_row = p_row0;
-      if (warp == 2) DAD_TRACE(0);
 
       // ---- p = exp2(s * scale * log2e - m), one FFMA + one MUFU per score; bf16 P goes
       // to shared memory in the swizzled K-major layout. A half-row with no visible key yet has
@@ -427,7 +413,6 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
       }
       tc_fence_before_sync();
       mbar_arrive(&bars->p_full);
-      if (warp == 2) DAD_TRACE(0);
     }
 
     // Epilogue: merge the two halves of each row. out = (O_0 w_0 + O_1 w_1) / (l_0 w_0 + l_1 w_1)
@@ -478,9 +463,6 @@ flash_fwd_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
   // ------------------------------ common exit ------------------------------
   tc_fence_before_sync();
   __syncthreads();
-#ifdef DADATTN_TRACE
-  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_trace[3][life_n_++] = clock64();
-#endif
   if (warp == 1) {
     __syncwarp();
     tc_fence_after_sync();
@@ -514,7 +496,6 @@ int launch_fwd_bf16(uint16_t* out, float* lse, const uint16_t* q, const uint16_t
 
 using namespace dadattn;
 
-DAD_TRACE_READER(dadattn_trace_read_fwd)
 
 extern "C" int dadattn_flash_bf16_supported(int d_head) { return d_head == 64 || d_head == 128; }
 

@@ -181,7 +181,6 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
       const SmemDescBase c1_desc0 = make_desc_base_sw128(smem_u32(smem + L::kC1), kSubPanelBytes);
       const SmemDescBase c2_desc0 = make_desc_base_sw128(smem_u32(smem + L::kC2), kSubPanelBytes);
       bool ok = mbar_wait(&bars->r_full, 0, abort_flag);
-      DAD_TRACE_DECL;
 
       // X1 = R1 C1^T, X2 = R2 C2^T for step i into score buffer i % kXBufs (the caller has made
       // sure that buffer is free)
@@ -191,7 +190,6 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
         const SmemDescBase c1{c1_desc0.lo + s * (L::kSub >> 4), c1_desc0.hi};
         const SmemDescBase c2{c2_desc0.lo + s * (L::kSub >> 4), c2_desc0.hi};
         if (!mbar_wait(&bars->c1_full[s], par, abort_flag)) return false;
-        DAD_TRACE(1);
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
@@ -207,7 +205,6 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
                  kk > 0 ? 1u : 0u);
         }
         mma_commit(&bars->x_full[xb]);
-        DAD_TRACE(1);
         return true;
       };
       // accumulators += (p | ds tiles of step i) . streamed tiles of step i (K = 64 rows)
@@ -216,7 +213,6 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
         const SmemDescBase c1{c1_desc0.lo + s * (L::kSub >> 4), c1_desc0.hi};
         const SmemDescBase c2{c2_desc0.lo + s * (L::kSub >> 4), c2_desc0.hi};
         if (!mbar_wait(&bars->w_full, i & 1, abort_flag)) return false;
-        DAD_TRACE(1);
         tc_fence_after_sync();
         // One MMA per 16 streamed rows covers all D output columns: the streamed tile is
         // MN-major and its 64-column panels are kSubPanelBytes apart (the descriptor's LBO).
@@ -229,7 +225,6 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
         }
         mma_commit(&bars->c_empty[s]);
         mma_commit(&bars->acc_done);
-        DAD_TRACE(1);
         return true;
       };
 
@@ -282,10 +277,8 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
       }
     }
     bool ok = true;
-    DAD_TRACE_DECL;
 
     for (int i = 0; i < n_it; ++i) {
-      if (warp == 2) DAD_TRACE(0);
       const int col0 = (first + i) * kSubRows;  // first query (KV) / key (dQ) of the streamed tile
       // sub-tiles that straddle the diagonal need the causal comparison
       const bool diagonal = KV ? (i < 2) : (first + i >= 2 * own);
@@ -306,7 +299,6 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
         if (!(ok = mbar_wait(&bars->vec_full, i & 1, abort_flag))) break;
       }
       if (!(ok = mbar_wait(&bars->x_full[xb], (i / kXBufs) & 1, abort_flag))) break;
-      if (warp == 2) DAD_TRACE(0);
       tc_fence_after_sync();
 
       const int cbase = half * 32;  // this thread's columns within the 64
@@ -316,7 +308,6 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
       tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive(&bars->x_free[xb]);  // scores are in registers: the buffer may be overwritten
-      if (warp == 2) DAD_TRACE(0);
 
       uint32_t pw[16], dw[16];
 #pragma unroll
@@ -358,9 +349,7 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
         dw[c / 2 + 1] = pack_bf16(dv[2], dv[3]);
       }
       // the previous step's p / ds tiles must have been consumed before they are overwritten
-      if (warp == 2) DAD_TRACE(0);
       if (i > 0 && !(ok = mbar_wait(&bars->acc_done, (i - 1) & 1, abort_flag))) break;
-      if (warp == 2) DAD_TRACE(0);
 #pragma unroll
       for (int v4 = 0; v4 < 4; ++v4) {
         const int chunk = half * 4 + v4;  // 16-byte chunk within the 128-byte row
@@ -373,7 +362,6 @@ flash_bwd_bf16_kernel(const __grid_constant__ CUtensorMap map_r1,
       }
       fence_proxy_async_smem();
       mbar_arrive(&bars->w_full);
-      if (warp == 2) DAD_TRACE(0);
     }
 
     // Epilogue. dK/dV kernel: half 0 stores dV, half 1 stores dK. dQ kernel: halves split D.
@@ -481,7 +469,6 @@ thread_local int g_deterministic = 0;
 
 using namespace dadattn;
 
-DAD_TRACE_READER(dadattn_trace_read_bwd)
 
 extern "C" int dadattn_set_bwd_deterministic(int on) {
   g_deterministic = on ? 1 : 0;

@@ -267,7 +267,6 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const SmemDescBase p_t = make_desc_base_sw128(smem_u32(smem + L::kP), kFPanel);
       const SmemDescBase ds_t = make_desc_base_sw128(smem_u32(smem + L::kDS), kFPanel);
       const SmemDescBase ds_k = make_desc_base_sw128(smem_u32(smem + L::kDS), 0);
-      DAD_TRACE_DECL;
 
       // S = Q K^T and dP = dO V^T of tile g (counted over all items of this CTA), K / V buffer kb
       auto issue_x = [&](int g, int kb) -> bool {
@@ -287,7 +286,6 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int kk = 0; kk < D / 16; ++kk)
           mma_ss(tmem + kColDP, desc_at(dd, kk * 32), desc_at(vd, kk * 32), idesc_x, kk > 0 ? 1u : 0u);
         mma_commit(&bars->x_full);
-        DAD_TRACE(1);
         return true;
       };
       // dV += P^T dO, dK += dS^T Q (fresh accumulators on an item's first tile), dQ_tile = dS K
@@ -299,7 +297,6 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // w_full also says that the compute warps have taken the previous item's dK / dV out of
         // tensor memory
         if (!mbar_wait(&bars->w_full, g & 1, abort_flag)) return false;
-        DAD_TRACE(1);
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < kFT / 16; ++kk) {   // K dimension = 128 queries, 16 per MMA
@@ -319,7 +316,6 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         mma_commit(&bars->qdo_empty[s]);
         mma_commit(&bars->acc_done);
-        DAD_TRACE(1);
         return true;
       };
 
@@ -406,7 +402,6 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint8_t* ds_row = smem + L::kDS + (cg / 2) * kFPanel + row * 128;
     uint8_t* dq_row = smem + L::kDQ + (cg / 2) * kFPanel + row * 128;
     bool ok = true;
-    DAD_TRACE_DECL;
 
     // dQ of tile t: TMEM -> swizzled fp32 staging, which the reducer warp sends on. The caller
     // has seen acc_done of tile t.
@@ -499,13 +494,11 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const Item tn = decode_item(nxt < n_items ? nxt : 0, BH, n_tiles, group_bh);
           load_row(nxt < n_items, tn.kt, tn.bh, next_lse2, next_delta);
         }
-        if (warp == 2) DAD_TRACE(0);
         // (one barrier per buffer: the next completion of this one needs the GEMMs of tile g,
         // hence this thread's own P / dS, so its phase cannot run away from a slow waiter)
         if (!(ok = mbar_wait(&bars->vec_full[g & 1], (g >> 1) & 1, abort_flag))) break;
         const float row_lse2 = vbuf[row], row_delta_s = vbuf[128 + row];
         if (!(ok = mbar_wait(&bars->x_full, g & 1, abort_flag))) break;
-        if (warp == 2) DAD_TRACE(0);
         tc_fence_after_sync();
         // Sixteen columns at a time: the packed results have to wait in registers for the P / dS
         // buffers, and nothing here may spill (local memory shares the path the reduce-adds load).
@@ -519,7 +512,6 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (h == 1) {
             tc_fence_before_sync();
             mbar_arrive(&bars->x_free);  // scores are in registers: the next tile's GEMMs may overwrite
-            if (warp == 2) DAD_TRACE(0);
           }
           // ds = p (dP - delta) scale as p * fma(dP, scale, -delta scale); the causal compare
           // only exists on an item's first (diagonal) tile
@@ -557,13 +549,11 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
           }
         }
-        if (warp == 2) DAD_TRACE(0);
         // P / dS of tile g-1 consumed and its dQ complete in tensor memory
         if (g > 0) {
           if (!(ok = mbar_wait(&bars->acc_done, (g - 1) & 1, abort_flag))) break;
           tc_fence_after_sync();
         }
-        if (warp == 2) DAD_TRACE(0);
         // Across an item boundary tile g-1 also completed dK / dV of the previous item: take them
         // out of tensor memory before w_full lets this item's first GEMMs overwrite them.
         if (new_item) stage_dkv((j - 1) & 1);
@@ -578,7 +568,6 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         fence_proxy_async_smem();
         mbar_arrive(&bars->w_full);
-        if (warp == 2) DAD_TRACE(0);
         if (g > 0 && !(ok = drain_dq(g - 1))) break;
       }
       cur = nxt;
@@ -689,7 +678,6 @@ int make_dq_workspace_map(CUtensorMap* map, float* ws, int BH, int S) {
 
 }  // namespace
 }  // namespace dadattn
-DAD_TRACE_READER(dadattn_trace_read_fused)
 namespace dadattn {
 
 // Workspace: delta [BH,S] fp32, then the dQ accumulator [BH,S,64] fp32 (256-byte aligned), then

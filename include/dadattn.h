@@ -5,8 +5,18 @@
  * stream (pass NULL for the legacy default stream, which is what DadGPT itself uses) and
  * returns without synchronising. Return value: 0 on success, a negative DADATTN_E_* code
  * otherwise; dadattn_last_error() then describes the failure (thread-local string).
- * All tensors and workspaces belong to the caller; the library's only allocation is one 4-byte
- * status word per device (see dadattn_device_status), made on first use and kept until exit. There is no CPU fallback: without a CUDA device every compute call fails.
+ * All tensors and workspaces belong to the caller. What the library itself holds on a device:
+ *  - two 4-byte status words (see dadattn_device_status), allocated with cudaMalloc by the first
+ *    bf16, decode or fp32-decode call on that device and kept until exit. Because of that
+ *    allocation the FIRST such call on a device must come before any stream capture; later
+ *    calls allocate nothing;
+ *  - the grow-only buffer behind dadattn_library_scratch, only if that function is called;
+ *  - an 8 MiB array in the library image for dadattn_decode_bf16_noalloc (no allocation call).
+ * There is no CPU fallback: without a CUDA device every compute call fails.
+ *
+ * Device-side waits are bounded. If one runs out, the kernel records DADATTN_E_TIMEOUT and
+ * exits; copies and tensor-core operations it had in flight may still land afterwards, so every
+ * result enqueued on that device up to the next dadattn_device_status() call is void.
  *
  * Tensor layouts follow DadGPT: heads already split, [BH, S, D] contiguous, row-major;
  * lse / delta are [BH, S] fp32. "bf16" pointers are raw 16-bit bfloat16 (uint16_t here so the
@@ -198,22 +208,32 @@ int dadattn_decode_bf16(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
  * workspace: the split-K partials go to a fixed 8 MiB array inside the library image (held by
  * every GPU that loads the library, until exit). The call performs no cudaMalloc/cudaFree and
  * uses no allocating routine.
- *  - Limit: the array is 8 MiB (8388608 bytes): 64 KiB of tickets (B*H + 33 <= 16384)
- *    and the rest for records (none when B*H >= 592, where each CTA walks a whole sequence);
- *    dadattn_decode_workspace_bytes(B,H,D,max_len) tells what a shape needs, and shapes that
- *    need more than the array holds return DADATTN_E_WORKSPACE.
+ *  - Limit: the array is 8 MiB (8388608 bytes). Its first 64 KiB hold the tickets, which need
+ *    B*H + 33 <= 16384, i.e. B*H <= 16351: that is the binding limit for any shape with
+ *    B*H >= 592, where each CTA walks a whole sequence and there are no records at all. With
+ *    fewer (sequence, head) pairs the cache rows are split across CTAs and the records
+ *    (B*H*splits*(D+2)*4 bytes, at most ~5 splits) must fit in the remaining 8 MiB - 64 KiB,
+ *    which they do for every max_len up to about 100 000 rows at D = 64.
+ *    dadattn_decode_workspace_bytes(B,H,D,max_len) tells what a shape needs; shapes beyond the
+ *    array return DADATTN_E_WORKSPACE.
  *  - The first call on each device looks up the array's device address
  *    (cudaGetSymbolAddress); make that first call before starting any stream capture.
  *  - All calls share the one array and it keeps the previous call's contents. Only the tickets
  *    have to be zero when a call starts: they are zero when the library is loaded and every call
  *    hands them back zeroed (records are written before they are read within a call). Two calls
  *    that overlap on the GPU (different streams, or threads) race on the array: serialise them.
- *  - A sequence already at max_len is skipped as in dadattn_decode_bf16, but this variant has
- *    nowhere to report it (dadattn_device_status belongs to the allocating calls). */
+ *  - A sequence already at max_len is skipped as in dadattn_decode_bf16 and noted in a word
+ *    beside the array; dadattn_decode_noalloc_status reads it (dadattn_device_status belongs to
+ *    the allocating calls and does not see it). */
 int dadattn_decode_bf16_noalloc(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
                                 const uint16_t* v_new, uint16_t* k_cache, uint16_t* v_cache,
                                 int32_t* lengths, int B, int H, int D, int max_len, float scale,
                                 dadattn_stream_t stream);
+/* Waits for `stream`, then returns and clears the status word of dadattn_decode_bf16_noalloc on
+ * the current device: 0, or DADATTN_E_ARG when a call since the last read skipped a sequence
+ * whose length was outside [0, max_len). Copies from and to a symbol of the library image, so it
+ * allocates nothing either. No counterpart in the reference. */
+int dadattn_decode_noalloc_status(dadattn_stream_t stream);
 
 /* Synchronises the stream and returns the sticky device-side status word of this device
  * (0, or a DADATTN_E_* code recorded by a kernel: a bounded wait that ran out, a sequence at

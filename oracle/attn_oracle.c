@@ -8,7 +8,7 @@
  * The reference has no host attention function; its attention is a fixed sequence of primitive
  * ops (materialized branch of src/model.cpp). Each step below cites the reference code it
  * follows, including the order of the fp32 additions, so results agree with the reference's
- * own host functions bit for bit (checked by tests/test_oracle_vs_ref.py when the reference
+ * own host functions bit for bit (checked by tests/test_oracle.py when the reference
  * sources are available, and by the committed fixtures under tests/golden/ otherwise).
  *
  * Parity pin: the restatement is pinned against the reference's host functions

@@ -23,11 +23,22 @@ _u8p = np.ctypeslib.ndpointer(dtype=np.uint8, flags="C_CONTIGUOUS")
 _i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
 
 
+def reference_dir() -> str | None:
+    """Where the DadGPT source tree lies: $DADGPT_REFERENCE_DIR if set, else a directory named
+    ``reference`` beside this repository. None when neither holds the reference's ``src/``."""
+    env = os.environ.get("DADGPT_REFERENCE_DIR")
+    cands = [env] if env else [os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")]
+    for c in cands:
+        if c and os.path.isfile(os.path.join(c, "src", "tensor_ops.cpp")):
+            return os.path.abspath(c)
+    return None
+
+
 def build_oracle() -> str:
     """Compile liboracle.so (and the reference libraries when the reference tree exists)."""
     subprocess.run(["make", "-s", "-C", HERE, "all"], check=True)
-    ref = os.environ.get("DADGPT_REFERENCE_DIR", "/root/reference")
-    if os.path.isdir(os.path.join(ref, "src")):
+    ref = reference_dir()
+    if ref:
         subprocess.run(["make", "-s", "-C", HERE, "ref", f"REF={ref}"], check=True)
     return os.path.join(HERE, "liboracle.so")
 

@@ -1,6 +1,7 @@
 """Generates tests/golden/*.npz by running the REFERENCE's own host ops.
 
-Run where the reference tree is present (DADGPT_REFERENCE_DIR, default /root/reference):
+Run where the reference tree is present ($DADGPT_REFERENCE_DIR, or a directory named
+`reference` beside this repository):
 
     python tests/golden/make_golden.py
 

@@ -38,8 +38,29 @@ def test_no_compute_without_device_but_arguments_are_checked(lib):
     assert rc == -1 and b"outside context length" in lib.dadattn_last_error()
     # tickets (B*H + B uint32, padded to 256) + records [B*H][splits][D+2] fp32; 768 pairs fill
     # the GPU, so a CTA walks a whole sequence (1 split); 8 pairs get their rows split
-    assert lib.dadattn_decode_workspace_bytes(64, 12, 64, 1280) == 3328 + 64 * 12 * 1 * 66 * 4
+    assert lib.dadattn_decode_workspace_bytes(64, 12, 64, 1280) == 3328  # no records with 1 split
     assert lib.dadattn_decode_workspace_bytes(2, 4, 64, 1280) == 256 + 10752  # 8*5*66*4 padded to 256
+
+
+def test_noalloc_decode_limit_is_the_documented_one(lib):
+    # include/dadattn.h: the ticket area binds at B*H <= 16351 once each CTA walks a whole
+    # sequence (no records). The size check precedes every CUDA call, so it can be probed with
+    # dummy aligned pointers: one pair too many is E_WORKSPACE; at the limit the call gets past
+    # the check (and then fails for want of a device here, or would launch on a GPU box).
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("probes the host-side size check with dummy pointers; no-GPU boxes only")
+    p = 4096
+    for B, H in ((16352, 1), (1363, 12)):  # 16352 and 16356 pairs
+        rc = lib.dadattn_decode_bf16_noalloc(p, p, p, p, p, p, p, B, H, 64, 1280, 0.125, None)
+        assert rc == -5 and b"no-alloc" in lib.dadattn_last_error()
+    rc = lib.dadattn_decode_bf16_noalloc(p, p, p, p, p, p, p, 16351, 1, 64, 1280, 0.125, None)
+    assert rc == -3  # past the size check; no CUDA device in this process
+    # few pairs: rows are split (5 ways at max_len 1280) and the records count
+    assert lib.dadattn_decode_workspace_bytes(12, 12, 64, 1280) == 768 + 190208  # 144*5*66*4 padded to 256
+    # the records of a small-B*H call fit for any sensible cache length
+    rc = lib.dadattn_decode_bf16_noalloc(p, p, p, p, p, p, p, 2, 12, 64, 100000, 0.125, None)
+    assert rc == -3
 
 
 def test_gpuops_shim_defines_the_reference_symbols():
