@@ -11,15 +11,33 @@
 //   3. the same model with the drop-in switched to bf16 tensor-core arithmetic
 //      (dadattn_set_f32_precision(1)): fused against materialized at the bf16 bars (logits 2e-2,
 //      gradients 3e-2 relative L2), d_head 64.
+//   4. the reference's generation loop, generate_tokens (src/generate.cpp:94-139, compiled
+//      unmodified): greedy decoding of 8 tokens after a 300-token prompt on a model with
+//      ctx_len 512, so that model_prefill takes the fused forward (AttentionImpl::Auto), must
+//      give the tokens of the same model forced to AttentionImpl::Materialized.
+//   5. the reference's training loop, run_training (src/train.cpp:96-285, compiled unmodified),
+//      on a small synthetic token file: three optimizer steps with --attention fused against
+//      the same three steps with --attention materialized; the reported validation losses must
+//      agree to 1e-3 and a checkpoint must have been written.
 // Exit code 0 = all within tolerance; every figure is printed.
+#include <unistd.h>
+
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
+#include <filesystem>
+#include <iostream>
+#include <regex>
+#include <sstream>
 #include <vector>
 
 #include "dadattn.h"
+#include "dataloader.hpp"
+#include "generate.hpp"
 #include "gpu_ops.cuh"
 #include "model.hpp"
+#include "train.hpp"
 
 namespace {
 
@@ -136,6 +154,91 @@ bool prefill_then_cached(int d_model, int heads) {
   return ok;
 }
 
+// generate_tokens of the reference, prefill through the fused forward against materialized
+bool generation_loop_matches() {
+  const int prompt = 300, total = 308;
+  std::vector<uint16_t> seed(prompt);
+  for (int i = 0; i < prompt; ++i) seed[i] = static_cast<uint16_t>((i * 13 + 7) % 20);
+  std::vector<uint16_t> got[2];
+  const AttentionImpl impl[2] = {AttentionImpl::Auto, AttentionImpl::Materialized};
+  for (int r = 0; r < 2; ++r) {
+    ModelConfig config = make_config(1, 128, 2, 512);  // d_head 64; ctx 512: Auto means fused
+    Model model{};
+    model_alloc(model, config);
+    model.training = false;
+    model.attention = impl[r];
+    // greedy (temperature 0), no stop token inside the vocabulary
+    got[r] = generate_tokens(model, seed, 0.0f, 0, total, 1.0f, /*stop_token=*/60000);
+    model_free(model);
+  }
+  bool ok = got[0].size() == static_cast<size_t>(total) && got[0] == got[1];
+  std::printf("generate_tokens fused-prefill vs materialized: %zu tokens, last 8 =", got[0].size());
+  for (size_t i = got[0].size() >= 8 ? got[0].size() - 8 : 0; i < got[0].size(); ++i)
+    std::printf(" %d", static_cast<int>(got[0][i]));
+  std::printf(" %s\n", ok ? "OK" : "FAIL");
+  return ok;
+}
+
+// run_training of the reference on a synthetic token stream; returns the last reported val loss
+bool training_loop_runs() {
+  namespace fs = std::filesystem;
+  double val[2] = {NAN, NAN};
+  bool wrote_checkpoint = true;
+  const char* attention[2] = {"fused", "materialized"};
+  for (int r = 0; r < 2; ++r) {
+    fs::path dir = fs::temp_directory_path() / ("dadattn_link_check_" + std::to_string(getpid()) + "_" + attention[r]);
+    fs::remove_all(dir);
+    fs::create_directories(dir);
+    DatasetMeta meta;
+    meta.vocab_size = 64;
+    write_dataset_meta(dir.string(), meta);
+    std::vector<uint16_t> stream(40000);
+    unsigned x = 12345u;
+    for (auto& t : stream) {
+      x = x * 1664525u + 1013904223u;
+      t = static_cast<uint16_t>((x >> 16) % 64);
+    }
+    write_token_file((dir / "train.bin").string(), stream);
+    write_token_file((dir / "val.bin").string(), std::vector<uint16_t>(stream.begin(), stream.begin() + 6000));
+    TrainConfig tc;
+    tc.data_dir = dir.string();
+    tc.model = "tiny";
+    tc.d_model = 128;
+    tc.n_layers = 2;
+    tc.n_heads = 2;       // d_head 64
+    tc.seq_len = 512;
+    tc.batch_size = 2;
+    tc.max_steps = 3;
+    tc.warmup_steps = 1;
+    tc.dropout_rate = 0.0f;  // with dropout the reference never takes the fused path
+    tc.precision = "fp32";
+    tc.attention = attention[r];
+    tc.log_interval = 1;
+    tc.eval_interval = 1000;
+    tc.eval_batches = 2;
+    tc.checkpoint_interval = 0;
+    std::ostringstream captured;
+    std::streambuf* old = std::cout.rdbuf(captured.rdbuf());
+    try {
+      run_training(tc);
+    } catch (...) {
+      std::cout.rdbuf(old);
+      throw;
+    }
+    std::cout.rdbuf(old);
+    std::smatch m;
+    const std::string text = captured.str();
+    if (std::regex_search(text, m, std::regex("val_loss ([0-9.eE+-]+)"))) val[r] = std::atof(m[1].str().c_str());
+    wrote_checkpoint &= fs::exists(dir / "checkpoint_step_3.bin") && text.find("Training complete!") != std::string::npos;
+    fs::remove_all(dir);
+  }
+  gpu_set_matmul_precision(MatmulPrecision::FP32);
+  bool ok = wrote_checkpoint && std::isfinite(val[0]) && std::fabs(val[0] - val[1]) <= 1e-3;
+  std::printf("run_training 3 steps fused vs materialized: val_loss %.6f vs %.6f checkpoint=%d %s\n", val[0],
+              val[1], wrote_checkpoint ? 1 : 0, ok ? "OK" : "FAIL");
+  return ok;
+}
+
 }  // namespace
 
 int main() {
@@ -152,6 +255,8 @@ int main() {
     std::printf("supported(48)=%d supported(64)=%d\n", gpu_flash_attention_supported(48) ? 1 : 0,
                 gpu_flash_attention_supported(64) ? 1 : 0);
     ok &= !gpu_flash_attention_supported(48) && gpu_flash_attention_supported(64);
+    ok &= generation_loop_matches();
+    ok &= training_loop_runs();
   } catch (const std::exception& e) {
     std::printf("exception: %s\n", e.what());
     return 2;

@@ -121,3 +121,59 @@ def test_full_sequence_is_skipped_and_reported(cuda):
     assert device_status() == -1          # DADATTN_E_ARG recorded by the kernel, no fault
     assert cache.lengths.tolist() == [4, 16]
     assert (out[1] == 0).all() and device_status() == 0
+
+
+@pytest.mark.parametrize("graph", [False, True], ids=["plain", "graph"])
+def test_decode_at_the_benchmark_configuration(cuda, oracle, graph):
+    """The exact decode configuration bench.py times: 64 sequences, 12 heads, head size 64,
+    max_len 1280, lengths from seed 3 (every CTA walks a whole sequence, sequences taken longest
+    first), several appended steps, once through plain calls and once replayed from a captured
+    CUDA graph as the benchmark does. Output, appended cache rows and lengths are checked
+    against the CPU oracle after every step."""
+    from dadgpt_b200 import workloads as W
+    cfg = W.DecodeShape()
+    lens0 = W.decode_lengths(cfg)
+    assert (cfg.B, cfg.H, cfg.D, cfg.max_len) == (64, 12, 64, 1280) and lens0.max() <= 1024
+    cache = dad.KVCacheBF16(cfg.B, cfg.H, cfg.max_len, cfg.D, device=cuda)
+    gen = torch.Generator(device=cuda).manual_seed(cfg.seed)
+    cache.k.copy_(torch.randn(cache.k.shape, device=cuda, generator=gen))
+    cache.v.copy_(torch.randn(cache.v.shape, device=cuda, generator=gen))
+    cache.lengths.copy_(torch.from_numpy(lens0))
+    q, kn, vn = (torch.empty(cfg.B, cfg.H, cfg.D, dtype=torch.bfloat16, device=cuda) for _ in range(3))
+    out = torch.empty_like(q)
+
+    def fresh_token():
+        for t in (q, kn, vn):
+            t.copy_(torch.randn(t.shape, device=cuda, generator=gen))
+
+    fresh_token()
+    if graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            dad.decode_attention_bf16(out, q, kn, vn, cache, cfg.scale)  # first call outside capture
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                dad.decode_attention_bf16(out, q, kn, vn, cache, cfg.scale)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        cache.lengths.copy_(torch.from_numpy(lens0))  # undo the warm-up call's advance
+        step = g.replay
+    else:
+        def step():
+            dad.decode_attention_bf16(out, q, kn, vn, cache, cfg.scale)
+    for s in range(4):
+        fresh_token()
+        out.fill_(float("nan"))
+        step()
+        torch.cuda.synchronize()
+        now = lens0 + s + 1
+        assert (cache.lengths.cpu().numpy() == now).all()
+        kc, vc = cache.k.float().cpu().numpy(), cache.v.float().cpu().numpy()
+        for b in range(cfg.B):  # the appended rows hold the new token, bit for bit
+            assert torch.equal(cache.k[b, :, int(now[b]) - 1], kn[b])
+            assert torch.equal(cache.v[b, :, int(now[b]) - 1], vn[b])
+        want = oracle.decode(q.float().cpu().numpy(), kc, vc, now.astype(np.int32), cfg.scale)
+        assert max_abs(out.float().cpu().numpy(), want) <= 2e-2
+    assert device_status() == 0

@@ -1,9 +1,13 @@
-"""GPU: the reference's own model code (src/model.cpp, cuda/gpu_ops.cu, compiled unmodified)
+"""GPU: the reference's own model, training and generation code (src/model.cpp, src/train.cpp,
+src/generate.cpp, cuda/gpu_ops.cu, compiled unmodified; only the PCRE2 tokenizer is a link stub)
 linked against libdadattn_gpuops.so in place of its cuda/attention.cu (oracle/Makefile target
 _ref/ref_model_link_check). Reproduces, at the model level, the relations the reference's tests
 pin for this path: fused == materialized (tests/test_backward.cpp:432-480) and prefill + cached
 decode == full forward (tests/test_model.cpp:375-414), both at 1e-4; and fused == materialized
-once more with the drop-in switched to bf16 tensor-core arithmetic, at the bf16 tolerances."""
+once more with the drop-in switched to bf16 tensor-core arithmetic, at the bf16 tolerances. Then
+the reference's generate_tokens (src/generate.cpp:94-139; greedy tokens after a fused prefill equal
+those of the materialized model) and its run_training (src/train.cpp:96-285; three optimizer steps
+on a synthetic token file, fused against materialized validation loss)."""
 import os
 import subprocess
 
@@ -17,9 +21,12 @@ BIN = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), 
 def test_reference_model_runs_on_our_kernels(cuda):
     if not os.path.exists(BIN):
         pytest.skip("oracle/_ref/ref_model_link_check not built (reference tree absent at build time)")
-    r = subprocess.run([BIN], capture_output=True, text=True, timeout=300)
+    r = subprocess.run([BIN], capture_output=True, text=True, timeout=600)
     print(r.stdout, r.stderr)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "ALL OK" in r.stdout
-    assert r.stdout.count(" OK") >= 5
+    assert r.stdout.count(" OK") >= 7
     assert "(bf16 tensor cores)" in r.stdout
+    lines = r.stdout.splitlines()
+    assert any(l.startswith("generate_tokens") and l.endswith(" OK") for l in lines)
+    assert any(l.startswith("run_training") and l.endswith(" OK") for l in lines)

@@ -133,3 +133,21 @@ def test_oracle_bit_equal_to_reference_host_ops(oracle, ref_host):
         for a, b in zip(oracle.backward(dout, q, k, v, scale, rate=0.1, seed=42),
                         ref_host.backward(dout, q, k, v, scale, rate=0.1, mask=mask)):
             assert np.array_equal(a, b)
+
+
+def test_numpy_whole_unit_restatement_equals_the_c_oracle(oracle):
+    """oracle/rowcheck.py (blockwise float64 numpy, used where the C loops would take minutes)
+    against the C restatement, including a block edge inside the sequence."""
+    from oracle.rowcheck import attention_unit
+    rng = np.random.default_rng(33)
+    for S, D, block in ((70, 64, 1024), (300, 32, 128), (257, 128, 64)):
+        q, k, v, do = (rng.standard_normal((1, S, D), dtype=np.float32) * 0.5 for _ in range(4))
+        scale = D ** -0.5
+        o, lse = oracle.forward(q, k, v, scale)
+        grads = oracle.backward(do, q, k, v, scale)
+        got = attention_unit(q[0], k[0], v[0], do[0], scale, block=block)
+        assert np.abs(got[0] - o[0]).max() < 1e-5 and np.abs(got[1] - lse[0]).max() < 1e-5
+        for a, b in zip(got[2:], grads):
+            assert np.linalg.norm(a - b[0]) / np.linalg.norm(b[0]) < 1e-5
+        fo, fl = attention_unit(q[0], k[0], v[0], None, scale, block=block)
+        assert np.array_equal(fo, got[0]) and np.array_equal(fl, got[1])
