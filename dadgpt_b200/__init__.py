@@ -10,6 +10,7 @@ from .attention import (  # noqa: F401
     decode_attention_bf16,
     decode_attention_f32,
     dropout_mask,
+    dropout_mask_bits,
     gpu_flash_attention_backward,
     gpu_flash_attention_backward_bf16,
     gpu_flash_attention_backward_via_bf16,

@@ -20,10 +20,14 @@ SIGNATURES = {
     "dadattn_flash_fwd_f32_dropout": (I, [P, P, P, P, P, I, I, I, F, F, U64, U64, I64, P]),
     "dadattn_flash_bwd_f32_dropout": (I, [P] * 10 + [I, I, I, F, F, U64, U64, I64, P]),
     "dadattn_dropout_mask": (I, [P, I64, F, U64, U64, I64, P]),
+    "dadattn_dropout_mask_bits_bytes": (SZ, [I, I]),
+    "dadattn_dropout_mask_bits": (I, [P, SZ, I, I, F, U64, U64, I64, P]),
     "dadattn_flash_bf16_supported": (I, [I]),
     "dadattn_flash_fwd_bf16": (I, [P, P, P, P, P, I, I, I, F, F, U64, U64, I64, P]),
     "dadattn_flash_bwd_bf16_workspace_bytes": (SZ, [I, I, I]),
     "dadattn_flash_bwd_bf16": (I, [P, P, P, P, SZ, P, P, P, P, P, P, I, I, I, F, F, U64, U64, I64, P]),
+    "dadattn_flash_fwd_bf16_masked": (I, [P, P, P, P, P, I, I, I, F, F, P, P]),
+    "dadattn_flash_bwd_bf16_masked": (I, [P, P, P, P, SZ, P, P, P, P, P, P, I, I, I, F, F, P, P]),
     "dadattn_set_bwd_deterministic": (I, [I]),
     "dadattn_set_stage_events": (I, [P, I]),
     "dadattn_flash_f32_via_bf16_workspace_bytes": (SZ, [I, I, I]),

@@ -67,14 +67,34 @@ def gpu_flash_attention_backward(dq, dk, dv, delta, dout, out, lse, q, k, v, BH,
 
 
 def gpu_flash_attention_forward_bf16(out, lse, q, k, v, BH, S, d_head, scale, *, rate=0.0,
-                                     seed=0, offset=0, unit0=0):
-    """bf16 tensor-core forward (tcgen05); same argument order as the fp32 call."""
+                                     seed=0, offset=0, unit0=0, mask_bits=None):
+    """bf16 tensor-core forward (tcgen05); same argument order as the fp32 call. With
+    ``mask_bits`` (from :func:`dropout_mask_bits`) the dropout mask is read, not drawn."""
     lib = _lib.load()
     for n, t in (("out", out), ("q", q), ("k", k), ("v", v)):
         _need(t, torch.bfloat16, (BH, S, d_head), n)
     _need(lse, torch.float32, (BH, S), "lse")
+    if mask_bits is not None:
+        _lib.check(lib.dadattn_flash_fwd_bf16_masked(_ptr(out), _ptr(lse), _ptr(q), _ptr(k), _ptr(v),
+                                                     BH, S, d_head, scale, rate, _ptr(mask_bits),
+                                                     _stream()))
+        return
     _lib.check(lib.dadattn_flash_fwd_bf16(_ptr(out), _ptr(lse), _ptr(q), _ptr(k), _ptr(v), BH, S,
                                           d_head, scale, rate, seed, offset, unit0, _stream()))
+
+
+def dropout_mask_bits(BH, S, rate, seed, offset=0, unit0=0, out=None):
+    """Bit-packed keep mask of the reference's attention dropout (cuda/gpu_ops.cu:712-734 drawn
+    per probability, here packed per 128 x 128 tile of the causal lower triangle) for the
+    ``mask_bits`` argument of the bf16 calls below. Returns the int32 device tensor."""
+    lib = _lib.load()
+    nbytes = int(lib.dadattn_dropout_mask_bits_bytes(BH, S))
+    if out is None:
+        out = torch.empty(nbytes // 4, dtype=torch.int32, device="cuda")
+    _need(out, torch.int32, None, "mask bits")
+    _lib.check(lib.dadattn_dropout_mask_bits(_ptr(out), out.numel() * 4, BH, S, rate, seed, offset,
+                                             unit0, _stream()))
+    return out
 
 
 def flash_backward_bf16_workspace_bytes(BH, S, d_head) -> int:
@@ -82,14 +102,21 @@ def flash_backward_bf16_workspace_bytes(BH, S, d_head) -> int:
 
 
 def gpu_flash_attention_backward_bf16(dq, dk, dv, workspace, dout, out, lse, q, k, v, BH, S,
-                                      d_head, scale, *, rate=0.0, seed=0, offset=0, unit0=0):
-    """bf16 tensor-core backward; ``workspace`` replaces the fp32 call's ``delta`` scratch."""
+                                      d_head, scale, *, rate=0.0, seed=0, offset=0, unit0=0,
+                                      mask_bits=None):
+    """bf16 tensor-core backward; ``workspace`` replaces the fp32 call's ``delta`` scratch. With
+    ``mask_bits`` (from :func:`dropout_mask_bits`) the dropout mask is read, not drawn."""
     lib = _lib.load()
     for n, t in (("dq", dq), ("dk", dk), ("dv", dv), ("dout", dout), ("out", out), ("q", q),
                  ("k", k), ("v", v)):
         _need(t, torch.bfloat16, (BH, S, d_head), n)
     _need(lse, torch.float32, (BH, S), "lse")
     nbytes = workspace.numel() * workspace.element_size()
+    if mask_bits is not None:
+        _lib.check(lib.dadattn_flash_bwd_bf16_masked(
+            _ptr(dq), _ptr(dk), _ptr(dv), _ptr(workspace), nbytes, _ptr(dout), _ptr(out), _ptr(lse),
+            _ptr(q), _ptr(k), _ptr(v), BH, S, d_head, scale, rate, _ptr(mask_bits), _stream()))
+        return
     _lib.check(lib.dadattn_flash_bwd_bf16(
         _ptr(dq), _ptr(dk), _ptr(dv), _ptr(workspace), nbytes, _ptr(dout), _ptr(out), _ptr(lse),
         _ptr(q), _ptr(k), _ptr(v), BH, S, d_head, scale, rate, seed, offset, unit0, _stream()))

@@ -70,6 +70,29 @@ __device__ __forceinline__ uint32_t philox_draw(const PhiloxKey& p, uint64_t sub
   return p.word == 0 ? c0 : p.word == 1 ? c1 : p.word == 2 ? c2 : c3;
 }
 
+// The same draw when the wanted word is the first of the block (offset a multiple of 4, as in
+// every call the reference makes): both halves of each 32 x 32 product come from one widening
+// multiply, the round keys are compile-time offsets of the seed, and the last round computes
+// only the word that is used.
+__device__ __forceinline__ uint32_t philox_draw_word0(const PhiloxKey& p, uint64_t subsequence) {
+  uint32_t c0 = p.c0, c1 = p.c1, c2 = static_cast<uint32_t>(subsequence),
+           c3 = static_cast<uint32_t>(subsequence >> 32);
+#pragma unroll
+  for (int r = 0; r < 9; ++r) {
+    const uint64_t p0 = static_cast<uint64_t>(0xD2511F53u) * c0;
+    const uint64_t p1 = static_cast<uint64_t>(0xCD9E8D57u) * c2;
+    const uint32_t k0 = p.k0 + static_cast<uint32_t>(r) * 0x9E3779B9u;
+    const uint32_t k1 = p.k1 + static_cast<uint32_t>(r) * 0xBB67AE85u;
+    const uint32_t n0 = static_cast<uint32_t>(p1 >> 32) ^ c1 ^ k0;
+    const uint32_t n2 = static_cast<uint32_t>(p0 >> 32) ^ c3 ^ k1;
+    c1 = static_cast<uint32_t>(p1);
+    c3 = static_cast<uint32_t>(p0);
+    c0 = n0;
+    c2 = n2;
+  }
+  return __umulhi(0xCD9E8D57u, c2) ^ c1 ^ (p.k0 + 9u * 0x9E3779B9u);
+}
+
 // true = keep. Same float arithmetic as curand_uniform followed by the reference's `r < rate`.
 __device__ __forceinline__ bool philox_keep(const PhiloxKey& p, uint64_t subsequence,
                                             float rate) {
@@ -77,6 +100,28 @@ __device__ __forceinline__ bool philox_keep(const PhiloxKey& p, uint64_t subsequ
                  2.3283064e-10f / 2.0f);
   return !(u < rate);
 }
+
+// ---- bit-packed dropout mask (dadattn_dropout_mask_bits) ----------------------------------------
+// One 16-byte record per (batch x head, 128-query tile qt, 128-key tile kt <= qt, query row of
+// the tile): bit i of 32-bit word w says whether the probability of key 32 w + i of the key tile
+// is kept (1) or dropped (0). Records of a tile are contiguous (2 KB), tiles of a (batch, head)
+// are numbered qt (qt + 1) / 2 + kt: only the causal lower triangle exists.
+constexpr int kMaskTile = 128;
+__host__ __device__ inline size_t mask_bits_record(int bh, int qt, int kt, int row, int n_tiles) {
+  const size_t n_tri = static_cast<size_t>(n_tiles) * (n_tiles + 1) / 2;
+  return (static_cast<size_t>(bh) * n_tri + static_cast<size_t>(qt) * (qt + 1) / 2 + kt) * kMaskTile + row;
+}
+inline size_t dropout_mask_bits_bytes(int BH, int S) {
+  const size_t n_tiles = (static_cast<size_t>(S) + kMaskTile - 1) / kMaskTile;
+  return static_cast<size_t>(BH) * (n_tiles * (n_tiles + 1) / 2) * kMaskTile * 16;
+}
+
+// Forward at head size 64 (flash_fwd64_sm100.cu). mask_bits != nullptr with rate > 0: keep bits
+// from dadattn_dropout_mask_bits; mask_bits == nullptr with rate > 0: the Philox mask is drawn
+// inside the kernel.
+int launch_fwd_bf16_d64(uint16_t* out, float* lse, const uint16_t* q, const uint16_t* k,
+                        const uint16_t* v, int BH, int S, float scale, float rate, uint64_t seed,
+                        uint64_t offset, int64_t unit0, const uint32_t* mask_bits, cudaStream_t st);
 
 // Launch with programmatic stream serialization: the grid may become resident while its
 // predecessor in the stream drains, runs its set-up (barriers, TMEM, descriptor prefetch), and

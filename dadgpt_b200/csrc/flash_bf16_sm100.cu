@@ -27,6 +27,7 @@
 #include <cuda_bf16.h>
 
 #include <cfloat>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -516,9 +517,33 @@ extern "C" int dadattn_flash_fwd_bf16(uint16_t* out, float* lse, const uint16_t*
     return fail(DADATTN_E_ARG, "bf16 tensors must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool drop = rate > 0.f;
-  if (D == 64)
+  if (D == 64) {
+    static const bool old_kernel = getenv("DADATTN_FWD64_OLD") != nullptr;
+    if (!old_kernel)
+      return launch_fwd_bf16_d64(out, lse, q, k, v, BH, S, scale, rate, seed, offset, unit0, nullptr, st);
     return drop ? launch_fwd_bf16<64, true>(out, lse, q, k, v, BH, S, scale, rate, seed, offset, unit0, st)
                 : launch_fwd_bf16<64, false>(out, lse, q, k, v, BH, S, scale, 0.f, 0, 0, 0, st);
+  }
   return drop ? launch_fwd_bf16<128, true>(out, lse, q, k, v, BH, S, scale, rate, seed, offset, unit0, st)
               : launch_fwd_bf16<128, false>(out, lse, q, k, v, BH, S, scale, 0.f, 0, 0, 0, st);
+}
+
+extern "C" int dadattn_flash_fwd_bf16_masked(uint16_t* out, float* lse, const uint16_t* q,
+                                             const uint16_t* k, const uint16_t* v, int BH, int S, int D,
+                                             float scale, float rate, const uint32_t* mask_bits,
+                                             dadattn_stream_t stream) {
+  if (!out || !lse || !q || !k || !v) return fail(DADATTN_E_ARG, "null tensor pointer");
+  if (!mask_bits || !aligned(mask_bits, 16))
+    return fail(DADATTN_E_ARG, "mask_bits must be a 16-byte aligned device pointer");
+  if (BH <= 0 || S <= 0) return fail(DADATTN_E_ARG, "BH=%d and S=%d must be positive", BH, S);
+  if (BH > 65535) return fail(DADATTN_E_UNSUPPORTED, "BH=%d exceeds 65535 per call", BH);
+  if (D != 64)
+    return fail(DADATTN_E_UNSUPPORTED, "a bit-packed dropout mask is taken at head size 64 only (got %d)", D);
+  if (!(rate > 0.0f && rate < 1.0f))
+    return fail(DADATTN_E_ARG, "the masked forward needs the rate the mask was drawn with, in (0,1)");
+  if (!(scale > 0.0f)) return fail(DADATTN_E_ARG, "bf16 forward needs scale > 0");
+  if (!aligned(out, 16) || !aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(lse, 4))
+    return fail(DADATTN_E_ARG, "bf16 tensors must be 16-byte aligned");
+  return launch_fwd_bf16_d64(out, lse, q, k, v, BH, S, scale, rate, 0, 0, 0, mask_bits,
+                             static_cast<cudaStream_t>(stream));
 }

@@ -140,7 +140,9 @@ struct ItemFeed {
   }
 };
 
-template <bool DROP>
+// DROP: 0 = no dropout, 1 = Philox drawn in the kernel, 2 = keep bits read from `mask_bits`
+// (dadattn_dropout_mask_bits; layout in common.cuh).
+template <int DROP>
 __global__ void __launch_bounds__(kFThreads, 1)
 flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
@@ -148,7 +150,7 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_dv, const float* __restrict__ lse,
                        const float* __restrict__ delta, int* __restrict__ item_counter, int BH, int S,
                        int group_bh, float scale, float rate, PhiloxKey rng, int64_t unit0,
-                       int* __restrict__ status) {
+                       const uint32_t* __restrict__ mask_bits, int* __restrict__ status) {
   using L = FusedSmem;
   constexpr int D = kFD;
   constexpr uint32_t kTmemCols = 512;
@@ -463,13 +465,22 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       dl = in ? delta[at] : 0.f;
     };
 
+    // Keep bits of this thread's 32 key columns for one tile: word cg of the row's record,
+    // fetched a tile ahead like the row scalars.
+    auto load_keep = [&](bool valid, int q_tile, int k_tile, int bh) -> uint32_t {
+      if (DROP != 2 || !valid) return 0u;
+      return __ldg(mask_bits + mask_bits_record(bh, q_tile, k_tile, row, n_tiles) * 4 + cg);
+    };
+
     ItemFeed feed{bars, abort_flag, 0};
     int cur = feed.fetch(n_items);
     int nxt = cur < n_items ? feed.fetch(n_items) : n_items;
     float next_lse2 = INFINITY, next_delta = 0.f;
+    uint32_t keep_word = 0u, next_keep = 0u;
     if (cur < n_items) {
       const Item t0 = decode_item(cur, BH, n_tiles, group_bh);
       load_row(true, t0.kt, t0.bh, next_lse2, next_delta);
+      if (DROP == 2) next_keep = load_keep(true, t0.kt, t0.kt, t0.bh);
     }
     int g = 0, j = 0;
 
@@ -488,11 +499,14 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           vbuf[128 + row] = next_delta * scale;
           mbar_arrive(&bars->vec_full[g & 1]);
         }
+        if (DROP == 2) keep_word = next_keep;
         if (i + 1 < t.n_it) {
           load_row(true, t.kt + i + 1, t.bh, next_lse2, next_delta);
+          if (DROP == 2) next_keep = load_keep(true, t.kt + i + 1, t.kt, t.bh);
         } else {
           const Item tn = decode_item(nxt < n_items ? nxt : 0, BH, n_tiles, group_bh);
           load_row(nxt < n_items, tn.kt, tn.bh, next_lse2, next_delta);
+          if (DROP == 2) next_keep = load_keep(nxt < n_items, tn.kt, tn.kt, tn.bh);
         }
         // (one barrier per buffer: the next completion of this one needs the GEMMs of tile g,
         // hence this thread's own P / dS, so its phase cannot run away from a slow waiter)
@@ -521,9 +535,13 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (masked && key > q) p = 0.f;
             float gr = __uint_as_float(x2[cc]);
             pd = p;
-            if (DROP) {
+            if (DROP == 1) {
               const uint64_t idx = (static_cast<uint64_t>(unit0 + t.bh) * S + q) * S + key;
               const float mk = (p != 0.f && philox_keep(rng, idx, rate)) ? keep_scale : 0.f;
+              pd = p * mk;
+              gr *= mk;
+            } else if (DROP == 2) {
+              const float mk = ((keep_word >> (h * 16 + cc)) & 1u) ? keep_scale : 0.f;
               pd = p * mk;
               gr *= mk;
             }
@@ -691,7 +709,7 @@ size_t fused_bwd_workspace_bytes(int BH, int S) {
 int launch_bwd_fused_d64(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspace, const uint16_t* dout,
                          const uint16_t* out, const float* lse, const uint16_t* q, const uint16_t* k,
                          const uint16_t* v, int BH, int S, float scale, float rate, uint64_t seed,
-                         uint64_t offset, int64_t unit0, cudaStream_t st) {
+                         uint64_t offset, int64_t unit0, const uint32_t* mask_bits, cudaStream_t st) {
   using BF = __nv_bfloat16;
   const size_t delta_bytes = (static_cast<size_t>(BH) * S * sizeof(float) + 255) / 256 * 256;
   const size_t dq_bytes = (static_cast<size_t>(BH) * S * kFD * sizeof(float) + 255) / 256 * 256;
@@ -728,12 +746,12 @@ int launch_bwd_fused_d64(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspa
   dim3 grid(static_cast<unsigned>(n_items < sms ? n_items : sms));
   int group_bh = 65536 / S;
   group_bh = group_bh < 1 ? 1 : (group_bh > 64 ? 64 : group_bh);
-  const bool drop = rate > 0.f;
-  auto kern = drop ? flash_bwd_fused_kernel<true> : flash_bwd_fused_kernel<false>;
+  auto kern = rate > 0.f ? (mask_bits ? flash_bwd_fused_kernel<2> : flash_bwd_fused_kernel<1>)
+                         : flash_bwd_fused_kernel<0>;
   DAD_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FusedSmem::kBytes));
   DAD_CUDA(launch_pdl(kern, grid, dim3(kFThreads), FusedSmem::kBytes, st, mq, mk, mv, mdo, mws, mdk, mdv,
                       lse, static_cast<const float*>(delta), item_counter, BH, S, group_bh, scale, rate,
-                      rng, unit0, status));
+                      rng, unit0, mask_bits, status));
   stage_event(2, st);
   const int64_t n8 = rows * kFD / 8;
   DAD_CUDA(launch_pdl(fused_convert_kernel, dim3(static_cast<unsigned>((n8 + 255) / 256)), dim3(256), 0,

@@ -1,0 +1,605 @@
+// bf16 fused causal attention forward for sm_100a, head size 64: a persistent kernel, one CTA
+// per SM, that works on TWO 128-row query tiles of one (batch, head) at a time.
+//
+// The arithmetic is that of the reference's flash_fwd_kernel (cuda/attention.cu:17-73: online
+// softmax over key tiles, lse = max + ln(sum) of the scaled scores) with bf16 operands and fp32
+// accumulation. What differs is the shape of the work. At head size 64 a 128x128 score tile
+// costs 640 clocks of tensor pipe but 1024 clocks of the exp2 unit and, written naively, more
+// than 1200 issue slots per scheduler: the softmax, not the MMAs, is what has to be fed. So:
+//   * a work item is a PAIR of adjacent query tiles (A = tile 2p, B = tile 2p + 1) of one
+//     (batch, head); both use the same K/V tiles from one shared-memory ring and each has its
+//     own softmax group. While group A computes exponentials the tensor pipe runs B's products
+//     and vice versa;
+//   * a group is 256 threads, TWO per query row: one takes key columns 0-63 of every tile, the
+//     other columns 64-127. Each half keeps its OWN running max / sum and its OWN output
+//     accumulator in tensor memory (split-K inside the CTA), so the two threads of a row never
+//     talk inside the loop; the halves are merged once per item, in the epilogue. Sixteen
+//     softmax warps, four per scheduler, are what hides the tensor-memory and exp2 latencies;
+//   * the probabilities never touch shared memory: a thread reads its 64 scores from tensor
+//     memory once, keeps them in registers for the max and the exponentials, and writes P back
+//     as packed bf16 over the first half of the same columns, from where the P V product takes
+//     it as its A operand;
+//   * scale-and-subtract and the row sums run as packed two-float instructions (fma.rn.f32x2,
+//     add.rn.f32x2) and the row max as three-input max: about 3 issue slots per score;
+//   * CTAs are persistent: barriers, tensor memory and descriptors are set up once, items are
+//     dealt out heaviest first in a fixed serpentine order (no global counter to reset), the
+//     next item's Q tiles and first K/V tiles are in flight while the current one finishes, and
+//     its first score products are issued before the current item's epilogue.
+//
+//   warp 0        TMA producer (Q pair double-buffered, K/V through a 4-stage ring)
+//   warp 1        MMA issuer of group A, owner of the tensor-memory allocation
+//   warp 18       MMA issuer of group B (one issuing thread per group: a group's products are
+//                 issued the moment its probabilities are ready, whatever the other group does)
+//   warps 2-9     softmax group A (2-5: key columns 0-63, 6-9: 64-127)
+//   warps 10-17   softmax group B likewise
+// Tensor memory: S_A [0,128) S_B [128,256); O of (group X, half h) at 256 + 64 (2 X + h);
+// P of half h aliases the first 32 columns of its half of S_X.
+//
+// Every mbarrier wait is bounded (sm100_ptx.cuh); on expiry the CTA raises its abort flag, all
+// roles fall through to the common exit, tensor memory is freed and DADATTN_E_TIMEOUT is left in
+// the device status word. No cluster launch, no multicast: each CTA loads its own tiles.
+#include <cuda_bf16.h>
+
+#include <cfloat>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace dadattn {
+namespace {
+
+using namespace ptx;
+
+constexpr int kT = 128;               // tile edge: query rows per group, keys per K/V tile
+constexpr int kHD = 64;               // head size
+constexpr int kPanel = 128 * 128;     // [128 rows][64 bf16]: 16 KB, 128-byte rows, swizzled
+constexpr int kKvStages = 4;
+constexpr int kFwd64Threads = 19 * 32;
+constexpr int kHalfThreads = 128;     // threads of one half of a softmax group
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleAt = 8.0f;    // log2 units: O is rescaled only when the max grew by 2^8
+
+struct F64Smem {
+  static constexpr int kQ = 0;                                // [2 items][A, B] panels
+  static constexpr int kK = kQ + 4 * kPanel;
+  static constexpr int kV = kK + kKvStages * kPanel;
+  static constexpr int kStat = kV + kKvStages * kPanel;      // float2 [group][half][128]: (max, sum)
+  static constexpr int kBars = kStat + 2 * 2 * 128 * 8;
+  static constexpr int kBytes = kBars + 512;
+};
+
+struct F64Bars {
+  uint64_t q_full[2], q_empty[2];
+  uint64_t k_full[kKvStages], v_full[kKvStages], kv_empty[kKvStages];
+  uint64_t s_full[2], p_full[2], o_done[2][2], o_free[2], stat_full[2];   // first index: group A / B
+  uint32_t tmem_base;
+  int abort_flag;
+};
+static_assert(sizeof(F64Bars) <= 512, "barrier block");
+
+// ---- packed two-float arithmetic and three-input max (sm_100) --------------------------------
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
+      ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+      "r"(r[15]), "r"(taddr)
+      : "memory");
+}
+
+// 2^x for two values on the FMA pipe: integer part through the float-rounding trick, fraction
+// in [-0.5, 0.5] through a cubic (relative error 6e-4, below bf16's half ulp of 2e-3).
+// Arguments below -125 (masked scores are -inf) give exactly 0, as ex2.approx.ftz does.
+__device__ __forceinline__ float2 ex2_poly2(float2 x0) {
+  const float2 x = make_float2(fmaxf(x0.x, -125.f), fmaxf(x0.y, -125.f));
+  const float2 big = make_float2(12582912.f, 12582912.f);  // 1.5 * 2^23
+  const float2 t = fadd2(x, big);
+  const float2 f = fadd2(x, make_float2(big.x - t.x, big.y - t.y));
+  float2 p = ffma2(f, make_float2(0.0555041087f, 0.0555041087f), make_float2(0.2402265070f, 0.2402265070f));
+  p = ffma2(p, f, make_float2(0.6931471806f, 0.6931471806f));
+  p = ffma2(p, f, make_float2(1.0f, 1.0f));
+  float2 r;
+  r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
+  if (x0.x < -125.f) r.x = 0.f;
+  if (x0.y < -125.f) r.y = 0.f;
+  return r;
+}
+
+// ---- work items --------------------------------------------------------------------------------
+// Item e (0 = heaviest): query-tile pair p = n_pairs - 1 - e / BH of (batch, head) e % BH.
+// CTA c of G takes, in order, the items k * G + (k even ? c : G - 1 - c): a serpentine deal of
+// the weight-sorted list, so that a CTA that got an early (heavy) item in one row gets a late
+// (light) one in the next. Every role computes the same list; nothing is shared or reset.
+struct F64Item {
+  int bh, qa, n_a, n_b, n_kv;   // n_b = 0 when the pair's second tile lies beyond the sequence
+  bool valid;
+};
+__device__ __forceinline__ F64Item f64_item(int k, int BH, int n_tiles, int n_items) {
+  const int G = static_cast<int>(gridDim.x), c = static_cast<int>(blockIdx.x);
+  const int e = k * G + ((k & 1) ? (G - 1 - c) : c);
+  F64Item it;
+  it.valid = e < n_items;
+  const int row = e / BH;
+  const int n_pairs = (n_tiles + 1) / 2;
+  it.bh = e - row * BH;
+  it.qa = 2 * (n_pairs - 1 - row);
+  it.n_a = it.qa + 1;
+  it.n_b = (it.qa + 1 < n_tiles) ? it.qa + 2 : 0;
+  it.n_kv = it.n_b ? it.n_b : it.n_a;
+  return it;
+}
+
+// DROP: 0 = no dropout, 1 = Philox drawn in the kernel, 2 = keep bits read from `mask_bits`.
+template <int DROP>
+__global__ void __launch_bounds__(kFwd64Threads, 1)
+flash_fwd64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                   float* __restrict__ lse, int BH, int S, float scale, float rate, PhiloxKey rng,
+                   int64_t unit0, const uint4* __restrict__ mask_bits, int* __restrict__ status) {
+  using L = F64Smem;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kColS = 0, kColO = 256;   // S_X at kColS + 128 X, O_(X,h) at kColO + 64 (2 X + h)
+
+  extern __shared__ __align__(1024) uint8_t smem[];
+  F64Bars* bars = reinterpret_cast<F64Bars*>(smem + L::kBars);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  // the warp index through a shuffle, so that the compiler knows it is uniform across the warp
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x / 32), 0);
+  const int lane = threadIdx.x % 32;
+  const int n_tiles = (S + kT - 1) / kT;
+  const int n_items = BH * ((n_tiles + 1) / 2);
+
+  if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled layouts need a 1024-byte aligned base
+    if (threadIdx.x == 0) atomicExch(status, DADATTN_E_CUDA);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->q_full[b], 1);
+      mbar_init(&bars->q_empty[b], 2);              // one arrival per issuer
+      mbar_init(&bars->s_full[b], 1);
+      mbar_init(&bars->p_full[b], 2 * kHalfThreads);
+      mbar_init(&bars->o_done[b][0], 1);
+      mbar_init(&bars->o_done[b][1], 1);
+      mbar_init(&bars->o_free[b], 2 * kHalfThreads);
+      mbar_init(&bars->stat_full[b], 2 * kHalfThreads);
+    }
+    for (int s = 0; s < kKvStages; ++s) {
+      mbar_init(&bars->k_full[s], 1);
+      mbar_init(&bars->v_full[s], 1);
+      mbar_init(&bars->kv_empty[s], 2);             // one arrival per issuer
+    }
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = bars->tmem_base;
+  // Set-up is done; from here on global memory is read, which the previous grid in the stream
+  // may have produced. Once every CTA of this grid is here the next grid may start its set-up.
+  pdl_wait();
+  pdl_launch_dependents();
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (elect_one()) {
+      prefetch_tensormap(&map_q);
+      prefetch_tensormap(&map_k);
+      prefetch_tensormap(&map_v);
+      int g = 0;  // K/V tiles loaded so far, over all items
+      bool ok = true;
+      for (int k = 0; ok; ++k) {
+        const F64Item it = f64_item(k, BH, n_tiles, n_items);
+        if (!it.valid) break;
+        const int qb = k & 1;
+        // the Q buffer frees when the last score product of the item before last has completed
+        if (k >= 2 && !mbar_wait(&bars->q_empty[qb], ((k >> 1) - 1) & 1, abort_flag)) break;
+        mbar_arrive_expect_tx(&bars->q_full[qb], it.n_b ? 2 * kPanel : kPanel);
+        tma_load_3d(smem + L::kQ + (qb * 2 + 0) * kPanel, &map_q, &bars->q_full[qb], 0, it.qa * kT, it.bh);
+        if (it.n_b)
+          tma_load_3d(smem + L::kQ + (qb * 2 + 1) * kPanel, &map_q, &bars->q_full[qb], 0,
+                      (it.qa + 1) * kT, it.bh);
+        for (int j = 0; j < it.n_kv; ++j, ++g) {
+          const int s = g % kKvStages, use = g / kKvStages;
+          if (use > 0 && !(ok = mbar_wait(&bars->kv_empty[s], (use - 1) & 1, abort_flag))) break;
+          mbar_arrive_expect_tx(&bars->k_full[s], kPanel);
+          tma_load_3d(smem + L::kK + s * kPanel, &map_k, &bars->k_full[s], 0, j * kT, it.bh);
+          mbar_arrive_expect_tx(&bars->v_full[s], kPanel);
+          tma_load_3d(smem + L::kV + s * kPanel, &map_v, &bars->v_full[s], 0, j * kT, it.bh);
+        }
+      }
+    }
+  } else if (warp == 1 || warp == 18) {
+    // ------------------------------ MMA issuers ------------------------------
+    // One issuing thread per group. Issuer X walks the K/V ring tiles of all items in order and,
+    // per tile g, issues O_X += P_X V(g) and then S_X = Q_X K(g+1)^T (the next tile's scores, also
+    // across an item boundary). A ring stage and a Q buffer are released by both issuers: each
+    // commits (or, where its group has nothing to do with the tile, simply arrives) once.
+    if (elect_one()) {
+      const int X = (warp == 1) ? 0 : 1;
+      constexpr uint32_t idesc_s = make_idesc_bf16(kT, kT, 0, 0);    // Q, K: K-major
+      constexpr uint32_t idesc_o = make_idesc_bf16(kT, kHD, 0, 1);   // P from TMEM, V MN-major
+      const SmemDescBase q_desc0 = make_desc_base_sw128(smem_u32(smem + L::kQ), 0);
+      const SmemDescBase k_desc0 = make_desc_base_sw128(smem_u32(smem + L::kK), 0);
+      const SmemDescBase v_desc0 = make_desc_base_sw128(smem_u32(smem + L::kV), 0);
+      const uint32_t tSx = tmem + kColS + X * 128, tOx = tmem + kColO + X * 2 * kHD;
+      int n_pv = 0;      // P V products of this group issued so far
+      int n_done = 0;    // items finished so far in which the group took part
+      bool ok = true;
+
+      // S_X = Q_X K^T for K/V ring tile g of the item in Q buffer qb
+      auto issue_s = [&](int qb, int g) {
+        const SmemDescBase qd{q_desc0.lo + (qb * 2 + X) * (kPanel >> 4), q_desc0.hi};
+        const SmemDescBase kd{k_desc0.lo + (g % kKvStages) * (kPanel >> 4), k_desc0.hi};
+#pragma unroll
+        for (int kk = 0; kk < kHD / 16; ++kk)
+          mma_ss(tSx, desc_at(qd, kk * 32), desc_at(kd, kk * 32), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(&bars->s_full[X]);
+      };
+      // O_(X,h) (+)= P_(X,h) V[64 h .. 64 h + 63] for ring tile g, both halves. P of half h sits
+      // in the first 32 columns of its half of S_X, 16 keys (8 columns of packed bf16 pairs) per
+      // MMA; V is MN-major, 16 keys = 2048 bytes further down.
+      auto issue_pv = [&](int g, bool first_of_item) -> bool {
+        // the epilogue of the group's previous item must have read O_X before it is overwritten
+        if (first_of_item && n_done > 0 && !mbar_wait(&bars->o_free[X], (n_done - 1) & 1, abort_flag))
+          return false;
+        if (!mbar_wait(&bars->p_full[X], n_pv & 1, abort_flag)) return false;
+        tc_fence_after_sync();
+        const SmemDescBase vd{v_desc0.lo + (g % kKvStages) * (kPanel >> 4), v_desc0.hi};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            mma_ts(tOx + h * kHD, tSx + h * 64 + kk * 8, desc_at(vd, (h * 4 + kk) * 2048), idesc_o,
+                   (!first_of_item || kk > 0) ? 1u : 0u);
+        }
+        mma_commit(&bars->o_done[X][n_pv & 1]);
+        ++n_pv;
+        return true;
+      };
+      auto n_of = [&](const F64Item& it) { return X ? it.n_b : it.n_a; };
+
+      F64Item cur = f64_item(0, BH, n_tiles, n_items);
+      F64Item nxt = f64_item(1, BH, n_tiles, n_items);
+      int g = 0;
+      if (cur.valid) {
+        ok = mbar_wait(&bars->q_full[0], 0, abort_flag) && mbar_wait(&bars->k_full[0], 0, abort_flag);
+        if (ok) {
+          tc_fence_after_sync();
+          if (n_of(cur) > 0) issue_s(0, 0);
+          if (n_of(cur) <= 1) {   // the item's only (or no) score product of this group
+            if (n_of(cur) == 1) mma_commit(&bars->q_empty[0]); else mbar_arrive(&bars->q_empty[0]);
+          }
+        }
+      }
+      for (int k = 0; ok && cur.valid; ++k) {
+        const int qb = k & 1;
+        const int n_x = n_of(cur);
+        for (int j = 0; ok && j < cur.n_kv; ++j, ++g) {
+          const int s = g % kKvStages;
+          // The tile after this one in the ring: the item's next tile, or the next item's first.
+          const bool last = (j + 1 == cur.n_kv);
+          const bool have_next = !last || nxt.valid;
+          const F64Item& ni = last ? nxt : cur;
+          const int nj = last ? 0 : j + 1, nqb = last ? (qb ^ 1) : qb;
+          // Every release below follows a wait on the matching "full" barrier of the same use,
+          // also where this group has nothing to do with the tile: an idle issuer must not run
+          // ahead and arrive twice within one phase of a release barrier.
+          bool issued = false;
+          ok = mbar_wait(&bars->v_full[s], (g / kKvStages) & 1, abort_flag);
+          if (ok && j < n_x) {
+            ok = issue_pv(g, j == 0);
+            issued = ok;
+          }
+          if (ok && have_next) {
+            const int n_next = n_of(ni);
+            if (last) ok = mbar_wait(&bars->q_full[nqb], ((k + 1) >> 1) & 1, abort_flag);
+            if (ok && nj < n_next) {
+              ok = mbar_wait(&bars->k_full[(g + 1) % kKvStages], ((g + 1) / kKvStages) & 1, abort_flag);
+              if (ok) {
+                tc_fence_after_sync();
+                issue_s(nqb, g + 1);
+                issued = true;
+                if (nj + 1 == n_next) mma_commit(&bars->q_empty[nqb]);   // the item's last scores of this group
+              }
+            } else if (ok && nj == 0) {
+              // the next item has no tile for this group: hand its Q buffer back
+              mbar_arrive(&bars->q_empty[nqb]);
+            }
+          }
+          // this issuer's share of the stage's release: after every product of its that reads it
+          if (ok) {
+            if (issued) mma_commit(&bars->kv_empty[s]); else mbar_arrive(&bars->kv_empty[s]);
+          }
+        }
+        if (n_x > 0) ++n_done;
+        cur = nxt;
+        nxt = f64_item(k + 2, BH, n_tiles, n_items);
+      }
+    }
+  } else {
+    // ------------------------------ softmax groups ------------------------------
+    const int X = (warp - 2) / 8;         // 0: group A (first tile of the pair), 1: group B (warps 2-17)
+    const int half = ((warp - 2) / 4) & 1;  // which 64 key columns of every tile
+    const int quad = warp % 4;            // TMEM lane quadrant this warp may touch
+    const int row = quad * 32 + lane;     // row within the tile = TMEM lane
+    const uint32_t tlane = tmem + (static_cast<uint32_t>(quad * 32) << 16);
+    const uint32_t tS = tlane + kColS + X * 128 + half * 64;
+    const float scale_log2 = scale * kLog2e;
+    const float keep_scale = DROP ? 1.0f / (1.0f - rate) : 1.0f;
+    int t = 0;        // score tiles this group has processed so far, over all items
+    int n_item = 0;   // items this group has taken part in
+    bool ok = true;
+
+    for (int k = 0; ok; ++k) {
+      const F64Item it = f64_item(k, BH, n_tiles, n_items);
+      if (!it.valid) break;
+      const int n_x = X ? it.n_b : it.n_a;
+      if (n_x == 0) continue;               // the pair's second tile lies beyond the sequence
+      const int qt = it.qa + X;
+      const int limit = row - half * 64;    // diagonal tile: column i of this half visible iff i <= limit
+      float m = -INFINITY;                  // running max of the scaled scores, log2 units
+      float2 l2 = make_float2(0.f, 0.f);    // running sum, two interleaved partial sums
+      uint2 keep = make_uint2(~0u, ~0u), keep_next = keep;
+      const uint2* bits2 = reinterpret_cast<const uint2*>(mask_bits);
+      if (DROP == 2) keep_next = __ldg(bits2 + mask_bits_record(it.bh, qt, 0, row, n_tiles) * 2 + half);
+
+      for (int j = 0; j < n_x; ++j, ++t) {
+        if (DROP == 2) {
+          keep = keep_next;   // fetched a tile ahead: its latency hides behind this tile's work
+          if (j + 1 < n_x)
+            keep_next = __ldg(bits2 + mask_bits_record(it.bh, qt, j + 1, row, n_tiles) * 2 + half);
+        }
+        if (!(ok = mbar_wait(&bars->s_full[X], t & 1, abort_flag))) break;
+        tc_fence_after_sync();
+        const bool diagonal = (j == n_x - 1);
+
+        // ---- the thread's 64 scores: read once, kept in registers for the max and the
+        // exponentials ----
+        uint32_t xa[32], xb[32];
+        auto load_scores = [&]() {
+          tmem_ld32(tS, xa);
+          tmem_ld32(tS + 32, xb);
+          tmem_wait_ld();
+          if (diagonal) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (i > limit) xa[i] = 0xff800000u;  // -inf
+              if (32 + i > limit) xb[i] = 0xff800000u;
+            }
+          }
+        };
+        load_scores();
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          mx0 = fmax3(mx0, __uint_as_float(xa[i]), __uint_as_float(xa[i + 1]));
+          mx1 = fmax3(mx1, __uint_as_float(xb[i]), __uint_as_float(xb[i + 1]));
+        }
+        const float mx = fmaxf(mx0, mx1) * scale_log2;   // scale > 0 commutes with max
+
+        // ---- lazy rescale: O and the sum move to a new max only when it grew by 2^8 ----
+        if (j == 0) {
+          m = mx;  // O is first written by an MMA that does not accumulate: nothing to rescale
+        } else if (__any_sync(0xffffffffu, mx > m + kRescaleAt)) {
+          // P V of this half's previous tile must have completed before O is touched
+          if (!(ok = mbar_wait(&bars->o_done[X][(t - 1) & 1], ((t - 1) >> 1) & 1, abort_flag))) break;
+          tc_fence_after_sync();
+          const float m_new = fmaxf(m, mx);
+          // m = -inf: nothing but zeros has been accumulated so far (every earlier column masked)
+          const float corr = (m == -INFINITY) ? 0.f : ex2(m - m_new);
+#pragma unroll 1
+          for (int c = 0; c < kHD / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tlane + kColO + (X * 2 + half) * kHD + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+            tmem_st32(tlane + kColO + (X * 2 + half) * kHD + c * 32, o);
+          }
+          tmem_wait_st();
+          l2 = fmul2(l2, make_float2(corr, corr));
+          m = m_new;
+          // read the scores again rather than keep 64 registers alive across this rare path
+          load_scores();
+        }
+
+        // ---- p = exp2(s * scale * log2e - m); P goes back to tensor memory as packed bf16
+        // pairs over the first 32 of this half's columns. A half-row with no visible key yet has
+        // m = -inf: its scores are all -inf and must give p = 0, not exp2(nan). ----
+        const float neg_m = (m == -INFINITY) ? 0.f : -m;
+        const float2 sl = make_float2(scale_log2, scale_log2), nm = make_float2(neg_m, neg_m);
+        float2 la = make_float2(0.f, 0.f), lb = la;   // this tile's sums, two independent chains
+        auto exps = [&](const uint32_t (&x)[32], uint32_t (&dst)[16], int c0, uint32_t bits) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float2 e = ffma2(make_float2(__uint_as_float(x[i]), __uint_as_float(x[i + 1])), sl, nm);
+            float2 p;
+            if ((i & 7) == 6) {   // one pair in four on the FMA pipe
+              p = ex2_poly2(e);
+            } else {
+              p.x = ex2(e.x);
+              p.y = ex2(e.y);
+            }
+            if (i & 2) lb = fadd2(lb, p); else la = fadd2(la, p);
+            if (DROP == 1) {
+              const uint64_t idx = (static_cast<uint64_t>(unit0 + it.bh) * S + qt * kT + row) * S + j * kT + c0 + i;
+              p.x = (p.x != 0.f && philox_keep(rng, idx, rate)) ? p.x * keep_scale : 0.f;
+              p.y = (p.y != 0.f && philox_keep(rng, idx + 1, rate)) ? p.y * keep_scale : 0.f;
+            } else if (DROP == 2) {
+              p.x = ((bits >> i) & 1u) ? p.x * keep_scale : 0.f;
+              p.y = ((bits >> (i + 1)) & 1u) ? p.y * keep_scale : 0.f;
+            }
+            dst[i / 2] = pack_bf16(p.x, p.y);
+          }
+        };
+        {
+          uint32_t pk[16];
+          exps(xa, pk, half * 64, keep.x);
+          tmem_st16(tS, pk);          // P of this half's keys 0..31 -> its columns 0..15
+        }
+        {
+          uint32_t pk[16];
+          exps(xb, pk, half * 64 + 32, keep.y);
+          tmem_st16(tS + 16, pk);     // keys 32..63 -> columns 16..31
+        }
+        l2 = fadd2(l2, fadd2(la, lb));
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(&bars->p_full[X]);
+      }
+      if (!ok) break;
+
+      // ---- epilogue: merge the two halves of each row. out = (O_0 w_0 + O_1 w_1) / (l_0 w_0 +
+      // l_1 w_1) with w_h = exp2(m_h - max(m_0, m_1)); lse in natural-log units of the scaled
+      // scores. Each thread of the pair writes 32 of the row's 64 outputs. ----
+      float2* stat = reinterpret_cast<float2*>(smem + L::kStat) + X * 256;   // [half][128]
+      const int r = qt * kT + row;          // query index
+      stat[half * 128 + row] = make_float2(m, l2.x + l2.y);
+      mbar_arrive(&bars->stat_full[X]);
+      if (!(ok = mbar_wait(&bars->stat_full[X], n_item & 1, abort_flag))) break;
+      // the group's last P V products (both halves)
+      if (!(ok = mbar_wait(&bars->o_done[X][(t - 1) & 1], ((t - 1) >> 1) & 1, abort_flag))) break;
+      tc_fence_after_sync();
+      const float2 s0 = stat[row], s1 = stat[128 + row];
+      const float m_tot = fmaxf(s0.x, s1.x);   // half 0 always sees key 0: finite
+      const float w0 = ex2(s0.x - m_tot);
+      const float w1 = (s1.x == -INFINITY) ? 0.f : ex2(s1.x - m_tot);
+      const float l_tot = s0.y * w0 + s1.y * w1;
+      const float f0 = w0 / l_tot, f1 = w1 / l_tot;
+      __nv_bfloat16* dst = out + (static_cast<size_t>(it.bh) * S + r) * kHD + half * 32;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {   // 16 output columns at a time
+        uint32_t oa[16], ob[16];
+        tmem_ld16(tlane + kColO + (X * 2 + 0) * kHD + half * 32 + c * 16, oa);
+        tmem_ld16(tlane + kColO + (X * 2 + 1) * kHD + half * 32 + c * 16, ob);
+        tmem_wait_ld();
+        if (c == 1) {
+          tc_fence_before_sync();
+          mbar_arrive(&bars->o_free[X]);   // O and the statistics have been read: the next item may start
+        }
+        if (r < S) {
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            float y[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              y[e] = __uint_as_float(oa[8 * i + e]) * f0 + __uint_as_float(ob[8 * i + e]) * f1;
+            *reinterpret_cast<uint4*>(dst + c * 16 + i * 8) = make_uint4(
+                pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]), pack_bf16(y[4], y[5]), pack_bf16(y[6], y[7]));
+          }
+        }
+      }
+      ++n_item;
+      if (r < S) {
+        if (half == 0) lse[static_cast<size_t>(it.bh) * S + r] = (m_tot + log2f(l_tot)) * kLn2;
+      }
+    }
+  }
+
+  // ------------------------------ common exit ------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+  if (threadIdx.x == 0 && bars->abort_flag) report_timeout(status, bars->abort_flag);
+}
+
+template <int DROP>
+int launch_fwd64(uint16_t* out, float* lse, const uint16_t* q, const uint16_t* k, const uint16_t* v,
+                 int BH, int S, float scale, float rate, uint64_t seed, uint64_t offset, int64_t unit0,
+                 const uint32_t* mask_bits, cudaStream_t st) {
+  CUtensorMap mq, mk, mv;
+  if (int rc = make_tensor_map_bf16(&mq, q, BH, S, kHD, kT)) return rc;
+  if (int rc = make_tensor_map_bf16(&mk, k, BH, S, kHD, kT)) return rc;
+  if (int rc = make_tensor_map_bf16(&mv, v, BH, S, kHD, kT)) return rc;
+  int* status = device_status_word();
+  if (!status) return DADATTN_E_CUDA;
+  int dev = 0, sms = 0;
+  DAD_CUDA(cudaGetDevice(&dev));
+  DAD_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int n_tiles = (S + kT - 1) / kT;
+  const long long n_items = static_cast<long long>(BH) * ((n_tiles + 1) / 2);
+  if (n_items > INT32_MAX / 2) return fail(DADATTN_E_UNSUPPORTED, "too many (query tile pair, batch x head) items");
+  auto kern = flash_fwd64_kernel<DROP>;
+  DAD_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, F64Smem::kBytes));
+  dim3 grid(static_cast<unsigned>(n_items < sms ? n_items : sms));
+  DAD_CUDA(launch_pdl(kern, grid, dim3(kFwd64Threads), F64Smem::kBytes, st, mq, mk, mv,
+                      reinterpret_cast<__nv_bfloat16*>(out), lse, BH, S, scale, rate,
+                      make_philox(seed, offset), unit0, reinterpret_cast<const uint4*>(mask_bits), status));
+  return DADATTN_OK;
+}
+
+}  // namespace
+
+// Forward at head size 64. mask_bits != nullptr: keep bits from dadattn_dropout_mask_bits;
+// otherwise rate > 0 draws the Philox mask inside the kernel.
+int launch_fwd_bf16_d64(uint16_t* out, float* lse, const uint16_t* q, const uint16_t* k, const uint16_t* v,
+                        int BH, int S, float scale, float rate, uint64_t seed, uint64_t offset,
+                        int64_t unit0, const uint32_t* mask_bits, cudaStream_t st) {
+  if (rate > 0.f && mask_bits)
+    return launch_fwd64<2>(out, lse, q, k, v, BH, S, scale, rate, 0, 0, 0, mask_bits, st);
+  if (rate > 0.f)
+    return launch_fwd64<1>(out, lse, q, k, v, BH, S, scale, rate, seed, offset, unit0, nullptr, st);
+  return launch_fwd64<0>(out, lse, q, k, v, BH, S, scale, 0.f, 0, 0, 0, nullptr, st);
+}
+
+}  // namespace dadattn

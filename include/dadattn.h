@@ -91,6 +91,23 @@ int dadattn_flash_bwd_f32_dropout(float* dq, float* dk, float* dv, float* delta,
 int dadattn_dropout_mask(uint8_t* mask, int64_t n, float rate, uint64_t seed, uint64_t offset,
                          int64_t first, dadattn_stream_t stream);
 
+/* The same mask, bit-packed for the fused bf16 kernels, lower triangle only. The reference
+ * materialises its mask as one byte per probability, [BH,S,S], and reads it back in the backward
+ * (src/model.cpp:406-415,595-602); drawing it costs ten Philox rounds per probability, far more
+ * than the attention arithmetic itself. This call draws it ONCE per (seed, offset, shape) into
+ * `bits`; dadattn_flash_fwd_bf16_masked and dadattn_flash_bwd_bf16_masked then read 2 KB per
+ * 128 x 128 tile instead of each repeating the draw. Layout: for every (batch x head bh, query
+ * tile qt, key tile kt <= qt) in the order bh, qt (qt + 1) / 2 + kt, 128 records of 16 bytes, one
+ * per query row of the tile; bit i of 32-bit word w of a record = key 128 kt + 32 w + i, 1 = kept.
+ * Bits above the diagonal and rows beyond S are 0. unit0 as in dadattn_flash_fwd_f32_dropout.
+ * `bits`: 16-byte aligned device buffer of at least dadattn_dropout_mask_bits_bytes(BH, S)
+ * bytes. No counterpart signature in the reference (its mask is gpu_dropout_forward's output,
+ * cuda/gpu_ops.cu:729-734). */
+size_t dadattn_dropout_mask_bits_bytes(int BH, int S);
+int dadattn_dropout_mask_bits(uint32_t* bits, size_t bits_bytes, int BH, int S, float rate,
+                              uint64_t seed, uint64_t offset, int64_t unit0,
+                              dadattn_stream_t stream);
+
 /* ---- bf16 tensor-core path (tcgen05 / TMEM / TMA) ---------------------------------------- */
 
 /* Head sizes the bf16 kernels cover (64, 128). */
@@ -117,6 +134,19 @@ int dadattn_flash_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* works
                            const uint16_t* v, int BH, int S, int D, float scale, float rate,
                            uint64_t seed, uint64_t offset, int64_t unit0,
                            dadattn_stream_t stream);
+
+/* dadattn_flash_fwd_bf16 / dadattn_flash_bwd_bf16 with the dropout mask taken from `mask_bits`
+ * (dadattn_dropout_mask_bits, drawn with the same BH, S, rate and the caller's seed, offset and
+ * unit0) instead of being drawn inside the kernels: same results bit for bit, a fraction of the
+ * time. Head size 64 only; the backward must be the single-pass one (the default). */
+int dadattn_flash_fwd_bf16_masked(uint16_t* out, float* lse, const uint16_t* q, const uint16_t* k,
+                                  const uint16_t* v, int BH, int S, int D, float scale, float rate,
+                                  const uint32_t* mask_bits, dadattn_stream_t stream);
+int dadattn_flash_bwd_bf16_masked(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspace,
+                                  size_t workspace_bytes, const uint16_t* dout, const uint16_t* out,
+                                  const float* lse, const uint16_t* q, const uint16_t* k,
+                                  const uint16_t* v, int BH, int S, int D, float scale, float rate,
+                                  const uint32_t* mask_bits, dadattn_stream_t stream);
 
 /* By default the backward is a single-pass kernel (one per head size) that forms the
  * probabilities once and adds each key tile's dQ contribution into an fp32 accumulator in the

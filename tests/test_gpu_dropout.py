@@ -48,3 +48,32 @@ def test_mask_bit_exact_vs_reference_kernel(cuda, oracle):
     assert np.array_equal(ref_mask[:50_000].cpu().numpy(), oracle.dropout_mask(50_000, 0.1, 42))
     # checksum of the full mask, stable across runs
     assert int(ref_mask.sum().item()) == int(mine.sum().item())
+
+
+@pytest.mark.parametrize("BH,S,unit0,seed,offset", [(3, 70, 0, 42, 0), (2, 300, 5, 42, 0), (2, 257, 1, 7, 6),
+                                                     (1, 1024, 190, 42, 0)])
+def test_bit_packed_mask_equals_the_byte_mask(cuda, BH, S, unit0, seed, offset):
+    """dadattn_dropout_mask_bits against dadattn_dropout_mask (itself pinned against the
+    reference's kernel above): every bit of the causal lower triangle equals the byte of the
+    reference's flat [BH,S,S] mask at ((unit0 + bh) S + r) S + c; everything else is 0."""
+    rate = 0.1
+    bits = dad.dropout_mask_bits(BH, S, rate, seed, offset, unit0)
+    full = torch.empty(BH * S * S, dtype=torch.uint8, device=cuda)
+    dad.dropout_mask(full, rate, seed, offset, unit0 * S * S)
+    torch.cuda.synchronize()
+    full = full.view(BH, S, S).cpu().numpy()
+    nt = (S + 127) // 128
+    words = bits.cpu().numpy().view(np.uint32).reshape(BH, nt * (nt + 1) // 2, 128, 4)
+    unpacked = ((words[..., None] >> np.arange(32, dtype=np.uint32)) & 1).astype(np.uint8)
+    unpacked = unpacked.reshape(BH, -1, 128, 128)  # [bh, tile, row, key]
+    want = np.zeros_like(unpacked)
+    for qt in range(nt):
+        for kt in range(qt + 1):
+            r0, c0 = qt * 128, kt * 128
+            blk = np.zeros((BH, 128, 128), np.uint8)
+            rr, cc = min(128, S - r0), min(128, S - c0)
+            blk[:, :rr, :cc] = full[:, r0:r0 + rr, c0:c0 + cc]
+            if qt == kt:
+                blk *= np.tril(np.ones((128, 128), np.uint8))
+            want[:, qt * (qt + 1) // 2 + kt] = blk
+    assert np.array_equal(unpacked, want)

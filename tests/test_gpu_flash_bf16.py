@@ -28,8 +28,10 @@ def fwd(q, k, v, scale, dev, **kw):
 
 
 @pytest.mark.parametrize("D", [64, 128])
-@pytest.mark.parametrize("S", [1, 31, 128, 129, 200, 256, 384, 700])
+@pytest.mark.parametrize("S", [1, 31, 128, 129, 200, 256, 384, 600, 700, 1100])
 def test_forward_shapes_against_oracle(cuda, oracle, S, D):
+    # (S = 600 and 1100: an odd number of 128-row tiles, so the last query-tile pair of the
+    # head-size-64 kernel has no second tile and walks more K/V tiles than its ring holds)
     rng = np.random.default_rng(17 * D + S)
     BH = 3
     q, k, v = (rng.standard_normal((BH, S, D), dtype=np.float32) for _ in range(3))
@@ -195,3 +197,66 @@ def test_backward_matches_fp32_kernel_on_same_inputs(cuda):
                                      f[2], BH, S, D, 0.125)
     for a, b in zip((dq, dk, dv), g32):
         assert rel_l2(a.float().cpu().numpy(), b.cpu().numpy()) <= 3e-2
+
+
+@pytest.mark.parametrize("BH,S,unit0", [(3, 200, 0), (2, 700, 4), (5, 1024, 187)])
+def test_bit_packed_dropout_mask_gives_the_same_results_as_drawing_in_the_kernels(cuda, BH, S, unit0):
+    """Forward and single-pass backward at head size 64 fed with dadattn_dropout_mask_bits
+    against the same calls drawing the Philox mask themselves: out, lse, dK and dV bit for bit
+    (dQ is summed in arrival order in both, so it is compared at 1e-2 relative L2)."""
+    D, scale, rate = 64, 0.125, 0.1
+    g = torch.Generator(device="cpu").manual_seed(BH * S)
+    tq, tk, tv, tdo = ((torch.randn(BH, S, D, generator=g) * 0.7).to(cuda).to(torch.bfloat16) for _ in range(4))
+    bits = dad.dropout_mask_bits(BH, S, rate, 42, 0, unit0)
+    ws = torch.empty(flash_backward_bf16_workspace_bytes(BH, S, D), dtype=torch.uint8, device=cuda)
+    res = []
+    for kw in (dict(rate=rate, seed=42, offset=0, unit0=unit0), dict(rate=rate, mask_bits=bits)):
+        out, lse = torch.full_like(tq, float("nan")), torch.full((BH, S), float("nan"), device=cuda)
+        dad.gpu_flash_attention_forward_bf16(out, lse, tq, tk, tv, BH, S, D, scale, **kw)
+        grads = [torch.full_like(tq, float("nan")) for _ in range(3)]
+        dad.gpu_flash_attention_backward_bf16(*grads, ws, tdo, out, lse, tq, tk, tv, BH, S, D, scale, **kw)
+        assert device_status() == 0
+        res.append([out, lse] + grads)
+    for name, a, b in zip(("out", "lse", "dq", "dk", "dv"), *res):
+        assert torch.isfinite(a.float()).all(), name
+        if name == "dq":
+            assert rel_l2(a.float().cpu().numpy(), b.float().cpu().numpy()) <= 1e-2
+        else:
+            assert torch.equal(a, b), name
+    # the mask actually drops something: the dropout-free forward differs
+    plain, lse0 = torch.empty_like(tq), torch.empty(BH, S, device=cuda)
+    dad.gpu_flash_attention_forward_bf16(plain, lse0, tq, tk, tv, BH, S, D, scale)
+    assert not torch.equal(plain, res[1][0]) and torch.equal(lse0, res[1][1])
+
+
+def test_masked_calls_reject_what_they_do_not_cover(cuda):
+    from dadgpt_b200 import _lib
+    BH, S = 1, 128
+    bits = dad.dropout_mask_bits(BH, S, 0.1, 42)
+    x = torch.zeros(BH, S, 128, dtype=torch.bfloat16, device=cuda)
+    lse = torch.zeros(BH, S, device=cuda)
+    with pytest.raises(_lib.DadAttnError, match="head size 64"):
+        dad.gpu_flash_attention_forward_bf16(x, lse, x, x, x, BH, S, 128, 0.1, rate=0.1, mask_bits=bits)
+    small = torch.zeros(4, dtype=torch.int32, device=cuda)
+    with pytest.raises(_lib.DadAttnError, match="bytes"):
+        dad.dropout_mask_bits(BH, S, 0.1, 42, out=small)
+
+
+def test_forward_many_single_tile_units(cuda, oracle):
+    """S = 128 with many (batch x head) units: every work item of the head-size-64 forward is a
+    lone query tile, every persistent CTA walks several items, and the second softmax group and
+    its issuer idle throughout (they must neither stall nor release buffers early)."""
+    BH, S, D, scale = 700, 128, 64, 0.125
+    g = torch.Generator(device="cpu").manual_seed(9)
+    tq, tk, tv = ((torch.randn(BH, S, D, generator=g) * 0.7).to(cuda).to(torch.bfloat16) for _ in range(3))
+    out, lse = torch.full_like(tq, float("nan")), torch.full((BH, S), float("nan"), device=cuda)
+    dad.gpu_flash_attention_forward_bf16(out, lse, tq, tk, tv, BH, S, D, scale)
+    assert device_status() == 0
+    units = [0, 147, 148, 295, 296, 699]
+    o_ref, lse_ref = oracle.forward(tq[units].float().cpu().numpy(), tk[units].float().cpu().numpy(),
+                                    tv[units].float().cpu().numpy(), scale)
+    assert max_abs(out[units].float().cpu().numpy(), o_ref) <= 2e-2
+    assert max_abs(lse[units].cpu().numpy(), lse_ref) <= 1e-2
+    o32, l32 = torch.empty(BH, S, D, device=cuda), torch.empty(BH, S, device=cuda)
+    dad.gpu_flash_attention_forward(o32, l32, tq.float(), tk.float(), tv.float(), BH, S, D, scale)
+    assert (out.float() - o32).abs().max().item() <= 2e-2 and (lse - l32).abs().max().item() <= 1e-2
