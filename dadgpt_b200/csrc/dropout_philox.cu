@@ -2,6 +2,8 @@
 // (reference cuda/gpu_ops.cu:712-727): element i is dropped iff the first Philox4x32-10 uniform
 // of curand_init(seed, subsequence = i, offset) is < rate. The reference launches one thread
 // per byte; here a thread produces 16 consecutive bytes and stores them with one 128-bit write.
+#include <cmath>
+
 #include "common.cuh"
 
 namespace dadattn {
@@ -42,10 +44,42 @@ __global__ void dropout_mask_kernel(uint8_t* __restrict__ mask, int64_t n, float
 // mask_bits_record). Entries above the diagonal and rows beyond the sequence stay 0 and cost no
 // draw. grid = (lower-triangle tiles, batch x head), 512 threads = 128 rows x 4 words, so a
 // CTA's stores are one contiguous 2 KB record block.
+//
+// The kernel is bound by instruction issue (ten Philox rounds per probability), so the draw is
+// stripped to what the reference's mask needs: the round keys come precomputed from the host
+// (kernel parameters, i.e. constant-bank operands: no per-draw additions, no registers), both
+// halves of each 32 x 32 product come from one widening multiply, the last round computes only
+// the word that is used, and "uniform < rate" is decided on the integer draw: the uniform is a
+// non-decreasing function of the draw (cvt.rn then one fma), so the dropped draws are exactly
+// those below a threshold that the host finds with the same float arithmetic.
+struct PhiloxRounds {
+  uint32_t k0[10], k1[9];   // key words of rounds 0..9 (the last round needs only k0)
+  uint32_t c0, c1;          // low counter words: offset / 4
+  uint32_t word;            // offset % 4: which word of the block is the draw
+  uint32_t drop_below;      // draws below this are dropped (uniform < rate)
+};
+
+__device__ __forceinline__ bool keep_word0(const PhiloxRounds& p, uint32_t s_lo, uint32_t s_hi) {
+  uint32_t c0 = p.c0, c1 = p.c1, c2 = s_lo, c3 = s_hi;
+#pragma unroll
+  for (int r = 0; r < 9; ++r) {
+    const uint64_t p0 = static_cast<uint64_t>(0xD2511F53u) * c0;
+    const uint64_t p1 = static_cast<uint64_t>(0xCD9E8D57u) * c2;
+    const uint32_t n0 = static_cast<uint32_t>(p1 >> 32) ^ c1 ^ p.k0[r];
+    const uint32_t n2 = static_cast<uint32_t>(p0 >> 32) ^ c3 ^ p.k1[r];
+    c1 = static_cast<uint32_t>(p1);
+    c3 = static_cast<uint32_t>(p0);
+    c0 = n0;
+    c2 = n2;
+  }
+  const uint32_t draw = __umulhi(0xCD9E8D57u, c2) ^ c1 ^ p.k0[9];
+  return draw >= p.drop_below;
+}
+
 template <bool WORD0>
 __global__ void __launch_bounds__(512)
-dropout_mask_bits_kernel(uint32_t* __restrict__ bits, int S, int n_tiles, float rate, PhiloxKey rng,
-                         int64_t unit0) {
+dropout_mask_bits_kernel(uint32_t* __restrict__ bits, int S, int n_tiles, float rate,
+                         const __grid_constant__ PhiloxRounds rounds, PhiloxKey rng, int64_t unit0) {
   // tile index -> (qt, kt) with qt (qt + 1) / 2 + kt = index
   const int idx = static_cast<int>(blockIdx.x);
   int qt = static_cast<int>((sqrtf(8.0f * static_cast<float>(idx) + 1.0f) - 1.0f) * 0.5f);
@@ -60,14 +94,40 @@ dropout_mask_bits_kernel(uint32_t* __restrict__ bits, int S, int n_tiles, float 
   if (q < S) {
     const uint64_t base = (static_cast<uint64_t>(unit0 + bh) * S + q) * S + key0;
     const int n = min(32, q - key0 + 1);   // keys key0 .. key0 + n - 1 are visible to query q
+    if (WORD0) {
+      const uint32_t lo = static_cast<uint32_t>(base), hi = static_cast<uint32_t>(base >> 32);
+      if (n == 32) {
+#pragma unroll 8
+        for (int i = 0; i < 32; ++i)
+          word |= (keep_word0(rounds, lo + i, hi + (lo + i < lo ? 1u : 0u)) ? 1u : 0u) << i;
+      } else {
 #pragma unroll 4
-    for (int i = 0; i < n; ++i) {
-      const uint32_t draw = WORD0 ? philox_draw_word0(rng, base + i) : philox_draw(rng, base + i);
-      const float u = fmaf(static_cast<float>(draw), 2.3283064e-10f, 2.3283064e-10f / 2.0f);
-      word |= (u < rate ? 0u : 1u) << i;
+        for (int i = 0; i < n; ++i)
+          word |= (keep_word0(rounds, lo + i, hi + (lo + i < lo ? 1u : 0u)) ? 1u : 0u) << i;
+      }
+    } else {
+#pragma unroll 4
+      for (int i = 0; i < n; ++i) word |= (philox_keep(rng, base + i, rate) ? 1u : 0u) << i;
     }
   }
   bits[mask_bits_record(bh, qt, kt, row, n_tiles) * 4 + w] = word;
+}
+
+// Smallest draw that is NOT dropped: the uniform fmaf(float(draw), 2^-32, 2^-33) of
+// curand_uniform is non-decreasing in the draw, so a binary search with the very same float
+// operations finds the threshold exactly. rate < 1 keeps the largest draw (its uniform is 1).
+uint32_t drop_threshold(float rate) {
+  auto dropped = [rate](uint32_t d) {
+    const float u = fmaf(static_cast<float>(d), 2.3283064e-10f, 2.3283064e-10f / 2.0f);
+    return u < rate;
+  };
+  if (!dropped(0)) return 0;
+  uint32_t lo = 0, hi = 0xFFFFFFFFu;   // dropped(lo), !dropped(hi)
+  while (hi - lo > 1) {
+    const uint32_t mid = lo + (hi - lo) / 2;
+    if (dropped(mid)) lo = mid; else hi = mid;
+  }
+  return hi;
 }
 
 }  // namespace
@@ -95,12 +155,21 @@ extern "C" int dadattn_dropout_mask_bits(uint32_t* bits, size_t bits_bytes, int 
   const long long n_tri = static_cast<long long>(n_tiles) * (n_tiles + 1) / 2;
   if (n_tri > 0x7fffffffLL) return fail(DADATTN_E_UNSUPPORTED, "dropout mask bits: S too large");
   const PhiloxKey rng = make_philox(seed, offset);
+  PhiloxRounds rounds;
+  for (int r = 0; r < 10; ++r) {
+    rounds.k0[r] = rng.k0 + static_cast<uint32_t>(r) * 0x9E3779B9u;
+    if (r < 9) rounds.k1[r] = rng.k1 + static_cast<uint32_t>(r) * 0xBB67AE85u;
+  }
+  rounds.c0 = rng.c0;
+  rounds.c1 = rng.c1;
+  rounds.word = rng.word;
+  rounds.drop_below = drop_threshold(rate);
   dim3 grid(static_cast<unsigned>(n_tri), static_cast<unsigned>(BH));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (rng.word == 0)
-    dropout_mask_bits_kernel<true><<<grid, 512, 0, st>>>(bits, S, n_tiles, rate, rng, unit0);
+    dropout_mask_bits_kernel<true><<<grid, 512, 0, st>>>(bits, S, n_tiles, rate, rounds, rng, unit0);
   else
-    dropout_mask_bits_kernel<false><<<grid, 512, 0, st>>>(bits, S, n_tiles, rate, rng, unit0);
+    dropout_mask_bits_kernel<false><<<grid, 512, 0, st>>>(bits, S, n_tiles, rate, rounds, rng, unit0);
   DAD_LAUNCH_CHECK("dropout_mask_bits_kernel");
   return DADATTN_OK;
 }

@@ -50,13 +50,16 @@ def test_mask_bit_exact_vs_reference_kernel(cuda, oracle):
     assert int(ref_mask.sum().item()) == int(mine.sum().item())
 
 
-@pytest.mark.parametrize("BH,S,unit0,seed,offset", [(3, 70, 0, 42, 0), (2, 300, 5, 42, 0), (2, 257, 1, 7, 6),
-                                                     (1, 1024, 190, 42, 0)])
-def test_bit_packed_mask_equals_the_byte_mask(cuda, BH, S, unit0, seed, offset):
+@pytest.mark.parametrize("BH,S,unit0,seed,offset,rate", [(3, 70, 0, 42, 0, 0.1), (2, 300, 5, 42, 0, 0.1),
+                                                          (2, 257, 1, 7, 6, 0.1), (1, 1024, 190, 42, 0, 0.1),
+                                                          (2, 200, 3, 0xDEADBEEFCAFEF00D, 8, 0.37),
+                                                          (1, 130, 0, 42, 4, 0.999)])
+def test_bit_packed_mask_equals_the_byte_mask(cuda, BH, S, unit0, seed, offset, rate):
     """dadattn_dropout_mask_bits against dadattn_dropout_mask (itself pinned against the
     reference's kernel above): every bit of the causal lower triangle equals the byte of the
-    reference's flat [BH,S,S] mask at ((unit0 + bh) S + r) S + c; everything else is 0."""
-    rate = 0.1
+    reference's flat [BH,S,S] mask at ((unit0 + bh) S + r) S + c; everything else is 0. Offsets
+    that are multiples of 4 take the stripped-down draw with the integer drop threshold, the
+    others the general one."""
     bits = dad.dropout_mask_bits(BH, S, rate, seed, offset, unit0)
     full = torch.empty(BH * S * S, dtype=torch.uint8, device=cuda)
     dad.dropout_mask(full, rate, seed, offset, unit0 * S * S)
