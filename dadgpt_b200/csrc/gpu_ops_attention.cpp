@@ -15,6 +15,7 @@
 #include <string>
 
 #include "dadattn.h"
+#include "dadattn_gpu_ops.hpp"
 
 bool gpu_flash_attention_supported(int d_head) { return d_head == 32 || d_head == 64; }
 
@@ -58,5 +59,40 @@ void gpu_flash_attention_backward(float* dq, float* dk, float* dv, float* delta,
   }
   if (dadattn_flash_bwd_f32(dq, dk, dv, delta, dout, out, lse, q, k, v, BH, S, d_head, scale,
                             nullptr) != DADATTN_OK)
+    throw std::runtime_error(std::string("CUDA error: ") + dadattn_last_error());
+}
+
+// ---- additions beyond the reference's three signatures (include/dadattn_gpu_ops.hpp) ----------
+
+void gpu_flash_attention_forward_dropout(float* out, float* lse, const float* q, const float* k,
+                                         const float* v, int BH, int S, int d_head, float scale,
+                                         float rate, unsigned long long seed) {
+  if (!gpu_flash_attention_supported(d_head))
+    throw std::runtime_error("flash attention: unsupported d_head " + std::to_string(d_head));
+  if (dadattn_flash_fwd_f32_dropout(out, lse, q, k, v, BH, S, d_head, scale, rate, seed, 0, 0, nullptr) !=
+      DADATTN_OK)
+    throw std::runtime_error(std::string("CUDA error: ") + dadattn_last_error());
+}
+
+void gpu_flash_attention_backward_dropout(float* dq, float* dk, float* dv, float* delta,
+                                          const float* dout, const float* out, const float* lse,
+                                          const float* q, const float* k, const float* v, int BH,
+                                          int S, int d_head, float scale, float rate,
+                                          unsigned long long seed) {
+  if (!gpu_flash_attention_supported(d_head))
+    throw std::runtime_error("flash attention: unsupported d_head " + std::to_string(d_head));
+  if (dadattn_flash_bwd_f32_dropout(dq, dk, dv, delta, dout, out, lse, q, k, v, BH, S, d_head, scale, rate,
+                                    seed, 0, 0, nullptr) != DADATTN_OK)
+    throw std::runtime_error(std::string("CUDA error: ") + dadattn_last_error());
+}
+
+void gpu_decode_attention(float* out, const float* q, const float* k_new, const float* v_new,
+                          float* k_cache, float* v_cache, int n_heads, int max_len, int d_head,
+                          int pos, float scale) {
+  if (pos < 0 || pos >= max_len)
+    throw std::out_of_range("gpu_decode_attention: pos " + std::to_string(pos) + " outside cache length " +
+                            std::to_string(max_len));
+  if (dadattn_decode_f32(out, q, k_new, v_new, k_cache, v_cache, n_heads, max_len, d_head, pos, scale,
+                         nullptr) != DADATTN_OK)
     throw std::runtime_error(std::string("CUDA error: ") + dadattn_last_error());
 }

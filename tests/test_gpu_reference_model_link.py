@@ -30,3 +30,23 @@ def test_reference_model_runs_on_our_kernels(cuda):
     lines = r.stdout.splitlines()
     assert any(l.startswith("generate_tokens") and l.endswith(" OK") for l in lines)
     assert any(l.startswith("run_training") and l.endswith(" OK") for l in lines)
+
+
+PATCHED = os.path.join(os.path.dirname(BIN), "ref_patched_check")
+
+
+def test_patched_reference_model_reaches_fused_dropout_and_one_launch_decode(cuda):
+    """The reference's model with the call-site edits of oracle/patch_reference.py (a patched copy
+    under oracle/_ref/patched; the reference tree is untouched): attention dropout runs on the
+    fused path with the seeds the materialized path would have used (same masks, same results,
+    no [B*H, ctx, ctx] buffers), and model_forward_cached's attention is one launch."""
+    if not os.path.exists(PATCHED):
+        pytest.skip("oracle/_ref/ref_patched_check not built (reference tree absent at build time)")
+    r = subprocess.run([PATCHED], capture_output=True, text=True, timeout=600)
+    print(r.stdout, r.stderr)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "ALL OK" in r.stdout
+    lines = r.stdout.splitlines()
+    assert sum(l.startswith("fused_dropout_vs_materialized") and l.endswith(" OK") for l in lines) == 2
+    assert sum(l.startswith("prefill_then_one_launch_decode") and l.endswith(" OK") for l in lines) == 2
+    assert any(l.startswith("cached_decode") and "ms/token" in l for l in lines)
