@@ -13,9 +13,11 @@ from .attention import (  # noqa: F401
     dropout_mask_bits,
     gpu_flash_attention_backward,
     gpu_flash_attention_backward_bf16,
+    gpu_flash_attention_backward_bf16_interleaved,
     gpu_flash_attention_backward_via_bf16,
     gpu_flash_attention_forward,
     gpu_flash_attention_forward_bf16,
+    gpu_flash_attention_forward_bf16_interleaved,
     gpu_flash_attention_forward_via_bf16,
     gpu_flash_attention_supported,
 )

@@ -28,6 +28,8 @@ SIGNATURES = {
     "dadattn_flash_bwd_bf16": (I, [P, P, P, P, SZ, P, P, P, P, P, P, I, I, I, F, F, U64, U64, I64, P]),
     "dadattn_flash_fwd_bf16_masked": (I, [P, P, P, P, P, I, I, I, F, F, P, P]),
     "dadattn_flash_bwd_bf16_masked": (I, [P, P, P, P, SZ, P, P, P, P, P, P, I, I, I, F, F, P, P]),
+    "dadattn_flash_fwd_bf16_strided": (I, [P, P, P, P, P, I, I, I, I, F, F, U64, U64, I64, P]),
+    "dadattn_flash_bwd_bf16_strided": (I, [P, P, P, P, SZ, P, P, P, P, P, P, I, I, I, I, F, F, U64, U64, I64, P]),
     "dadattn_set_bwd_deterministic": (I, [I]),
     "dadattn_set_stage_events": (I, [P, I]),
     "dadattn_flash_f32_via_bf16_workspace_bytes": (SZ, [I, I, I]),

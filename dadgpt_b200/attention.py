@@ -122,6 +122,32 @@ def gpu_flash_attention_backward_bf16(dq, dk, dv, workspace, dout, out, lse, q, 
         _ptr(q), _ptr(k), _ptr(v), BH, S, d_head, scale, rate, seed, offset, unit0, _stream()))
 
 
+def gpu_flash_attention_forward_bf16_interleaved(out, lse, q, k, v, B, H, S, d_head, scale, *, rate=0.0,
+                                                 seed=0, offset=0, unit0=0):
+    """bf16 forward on the activations as the projections leave them, [B*S, H*d_head] (reference
+    src/model.cpp:372-387): no gpu_split_heads / gpu_merge_heads copies around the call."""
+    lib = _lib.load()
+    for n, t in (("out", out), ("q", q), ("k", k), ("v", v)):
+        _need(t, torch.bfloat16, (B * S, H * d_head), n)
+    _need(lse, torch.float32, (B * H, S), "lse")
+    _lib.check(lib.dadattn_flash_fwd_bf16_strided(_ptr(out), _ptr(lse), _ptr(q), _ptr(k), _ptr(v), B, H, S,
+                                                  d_head, scale, rate, seed, offset, unit0, _stream()))
+
+
+def gpu_flash_attention_backward_bf16_interleaved(dq, dk, dv, workspace, dout, out, lse, q, k, v, B, H, S,
+                                                  d_head, scale, *, rate=0.0, seed=0, offset=0, unit0=0):
+    """Backward of the call above; every bf16 tensor is [B*S, H*d_head]."""
+    lib = _lib.load()
+    for n, t in (("dq", dq), ("dk", dk), ("dv", dv), ("dout", dout), ("out", out), ("q", q),
+                 ("k", k), ("v", v)):
+        _need(t, torch.bfloat16, (B * S, H * d_head), n)
+    _need(lse, torch.float32, (B * H, S), "lse")
+    nbytes = workspace.numel() * workspace.element_size()
+    _lib.check(lib.dadattn_flash_bwd_bf16_strided(
+        _ptr(dq), _ptr(dk), _ptr(dv), _ptr(workspace), nbytes, _ptr(dout), _ptr(out), _ptr(lse),
+        _ptr(q), _ptr(k), _ptr(v), B, H, S, d_head, scale, rate, seed, offset, unit0, _stream()))
+
+
 def flash_f32_via_bf16_workspace_bytes(BH, S, d_head) -> int:
     return int(_lib.load().dadattn_flash_f32_via_bf16_workspace_bytes(BH, S, d_head))
 

@@ -118,10 +118,11 @@ inline size_t dropout_mask_bits_bytes(int BH, int S) {
 
 // Forward at head size 64 (flash_fwd64_sm100.cu). mask_bits != nullptr with rate > 0: keep bits
 // from dadattn_dropout_mask_bits; mask_bits == nullptr with rate > 0: the Philox mask is drawn
-// inside the kernel.
+// inside the kernel. heads > 0: tensors are the interleaved [B*S, heads*64] activations.
 int launch_fwd_bf16_d64(uint16_t* out, float* lse, const uint16_t* q, const uint16_t* k,
                         const uint16_t* v, int BH, int S, float scale, float rate, uint64_t seed,
-                        uint64_t offset, int64_t unit0, const uint32_t* mask_bits, cudaStream_t st);
+                        uint64_t offset, int64_t unit0, const uint32_t* mask_bits, int heads,
+                        cudaStream_t st);
 
 // Launch with programmatic stream serialization: the grid may become resident while its
 // predecessor in the stream drains, runs its set-up (barriers, TMEM, descriptor prefetch), and

@@ -73,6 +73,26 @@ int make_tensor_map_bf16(CUtensorMap* map, const void* base, int BH, int S, int 
   return DADATTN_OK;
 }
 
+int make_tensor_map_bf16_units(CUtensorMap* map, const void* base, int units, int S, int D, int box_rows,
+                               const UnitLayout& lay) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(DADATTN_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const int heads = lay.heads, batch = units / lay.heads;
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S),
+                              static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
+  // a dimension of extent 1 still needs a legal stride (a multiple of 16 bytes)
+  const cuuint64_t head_stride = heads > 1 ? static_cast<cuuint64_t>(lay.head) * 2 : static_cast<cuuint64_t>(D) * 2;
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(lay.row) * 2, head_stride,
+                                 static_cast<cuuint64_t>(lay.batch) * 2};
+  const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(DADATTN_E_CUDA, "cuTensorMapEncodeTiled (4-D) failed (%d)", (int)r);
+  return DADATTN_OK;
+}
+
 namespace {
 
 using namespace ptx;
@@ -520,7 +540,7 @@ extern "C" int dadattn_flash_fwd_bf16(uint16_t* out, float* lse, const uint16_t*
   if (D == 64) {
     static const bool old_kernel = getenv("DADATTN_FWD64_OLD") != nullptr;
     if (!old_kernel)
-      return launch_fwd_bf16_d64(out, lse, q, k, v, BH, S, scale, rate, seed, offset, unit0, nullptr, st);
+      return launch_fwd_bf16_d64(out, lse, q, k, v, BH, S, scale, rate, seed, offset, unit0, nullptr, 0, st);
     return drop ? launch_fwd_bf16<64, true>(out, lse, q, k, v, BH, S, scale, rate, seed, offset, unit0, st)
                 : launch_fwd_bf16<64, false>(out, lse, q, k, v, BH, S, scale, 0.f, 0, 0, 0, st);
   }
@@ -544,6 +564,25 @@ extern "C" int dadattn_flash_fwd_bf16_masked(uint16_t* out, float* lse, const ui
   if (!(scale > 0.0f)) return fail(DADATTN_E_ARG, "bf16 forward needs scale > 0");
   if (!aligned(out, 16) || !aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(lse, 4))
     return fail(DADATTN_E_ARG, "bf16 tensors must be 16-byte aligned");
-  return launch_fwd_bf16_d64(out, lse, q, k, v, BH, S, scale, rate, 0, 0, 0, mask_bits,
+  return launch_fwd_bf16_d64(out, lse, q, k, v, BH, S, scale, rate, 0, 0, 0, mask_bits, 0,
+                             static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dadattn_flash_fwd_bf16_strided(uint16_t* out, float* lse, const uint16_t* q,
+                                              const uint16_t* k, const uint16_t* v, int B, int H, int S,
+                                              int D, float scale, float rate, uint64_t seed,
+                                              uint64_t offset, int64_t unit0, dadattn_stream_t stream) {
+  if (!out || !lse || !q || !k || !v) return fail(DADATTN_E_ARG, "null tensor pointer");
+  if (B <= 0 || H <= 0 || S <= 0) return fail(DADATTN_E_ARG, "B=%d, H=%d and S=%d must be positive", B, H, S);
+  if (static_cast<long long>(B) * H > 65535)
+    return fail(DADATTN_E_UNSUPPORTED, "B*H=%lld exceeds 65535 per call", static_cast<long long>(B) * H);
+  if (D != 64)
+    return fail(DADATTN_E_UNSUPPORTED, "interleaved [B*S, H*D] activations are taken at head size 64 only (got %d)", D);
+  if (!(rate >= 0.0f && rate < 1.0f))
+    return fail(DADATTN_E_ARG, "dropout rate %f outside [0,1)", static_cast<double>(rate));
+  if (!(scale > 0.0f)) return fail(DADATTN_E_ARG, "bf16 forward needs scale > 0");
+  if (!aligned(out, 16) || !aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(lse, 4))
+    return fail(DADATTN_E_ARG, "bf16 tensors must be 16-byte aligned");
+  return launch_fwd_bf16_d64(out, lse, q, k, v, B * H, S, scale, rate, seed, offset, unit0, nullptr, H,
                              static_cast<cudaStream_t>(stream));
 }

@@ -450,7 +450,7 @@ size_t fused_bwd_workspace_bytes(int BH, int S);
 int launch_bwd_fused_d64(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspace, const uint16_t* dout,
                          const uint16_t* out, const float* lse, const uint16_t* q, const uint16_t* k,
                          const uint16_t* v, int BH, int S, float scale, float rate, uint64_t seed,
-                         uint64_t offset, int64_t unit0, const uint32_t* mask_bits, cudaStream_t st);
+                         uint64_t offset, int64_t unit0, const uint32_t* mask_bits, int heads, cudaStream_t st);
 
 thread_local cudaEvent_t* g_stage_events = nullptr;
 thread_local int g_stage_event_count = 0;
@@ -494,7 +494,7 @@ static int flash_bwd_bf16_checked(uint16_t* dq, uint16_t* dk, uint16_t* dv, void
                                   const float* lse, const uint16_t* q, const uint16_t* k,
                                   const uint16_t* v, int BH, int S, int D, float scale, float rate,
                                   uint64_t seed, uint64_t offset, int64_t unit0,
-                                  const uint32_t* mask_bits, dadattn_stream_t stream) {
+                                  const uint32_t* mask_bits, int heads, dadattn_stream_t stream) {
   if (!dq || !dk || !dv || !workspace || !dout || !out || !lse || !q || !k || !v)
     return fail(DADATTN_E_ARG, "null tensor pointer");
   if (BH <= 0 || S <= 0) return fail(DADATTN_E_ARG, "BH=%d and S=%d must be positive", BH, S);
@@ -518,11 +518,14 @@ static int flash_bwd_bf16_checked(uint16_t* dq, uint16_t* dk, uint16_t* dv, void
   if (D == 64 && !g_deterministic) {
     if (!aligned(workspace, 256)) return fail(DADATTN_E_ARG, "backward workspace must be 256-byte aligned");
     return launch_bwd_fused_d64(dq, dk, dv, workspace, dout, out, lse, q, k, v, BH, S, scale, rate,
-                                seed, offset, unit0, mask_bits, st);
+                                seed, offset, unit0, mask_bits, heads, st);
   }
   if (mask_bits)
     return fail(DADATTN_E_UNSUPPORTED,
                 "a bit-packed dropout mask is taken by the single-pass head-size-64 backward only");
+  if (heads > 0)
+    return fail(DADATTN_E_UNSUPPORTED,
+                "interleaved [B*S, H*D] activations are taken by the single-pass head-size-64 backward only");
   if (D == 128 && !g_deterministic) {
     if (!aligned(workspace, 256)) return fail(DADATTN_E_ARG, "backward workspace must be 256-byte aligned");
     return launch_bwd_fused_d128(dq, dk, dv, workspace, dout, out, lse, q, k, v, BH, S, scale, rate,
@@ -547,7 +550,7 @@ extern "C" int dadattn_flash_bwd_bf16(uint16_t* dq, uint16_t* dk, uint16_t* dv, 
                                       float scale, float rate, uint64_t seed, uint64_t offset,
                                       int64_t unit0, dadattn_stream_t stream) {
   return flash_bwd_bf16_checked(dq, dk, dv, workspace, workspace_bytes, dout, out, lse, q, k, v, BH, S, D,
-                                scale, rate, seed, offset, unit0, nullptr, stream);
+                                scale, rate, seed, offset, unit0, nullptr, 0, stream);
 }
 
 extern "C" int dadattn_flash_bwd_bf16_masked(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspace,
@@ -560,5 +563,20 @@ extern "C" int dadattn_flash_bwd_bf16_masked(uint16_t* dq, uint16_t* dk, uint16_
     return fail(DADATTN_E_ARG, "mask_bits must be a 16-byte aligned device pointer");
   if (!(rate > 0.0f)) return fail(DADATTN_E_ARG, "the masked backward needs the rate the mask was drawn with (> 0)");
   return flash_bwd_bf16_checked(dq, dk, dv, workspace, workspace_bytes, dout, out, lse, q, k, v, BH, S, D,
-                                scale, rate, 0, 0, 0, mask_bits, stream);
+                                scale, rate, 0, 0, 0, mask_bits, 0, stream);
+}
+
+extern "C" int dadattn_flash_bwd_bf16_strided(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspace,
+                                              size_t workspace_bytes, const uint16_t* dout,
+                                              const uint16_t* out, const float* lse, const uint16_t* q,
+                                              const uint16_t* k, const uint16_t* v, int B, int H, int S, int D,
+                                              float scale, float rate, uint64_t seed, uint64_t offset,
+                                              int64_t unit0, dadattn_stream_t stream) {
+  if (B <= 0 || H <= 0) return fail(DADATTN_E_ARG, "B=%d and H=%d must be positive", B, H);
+  if (static_cast<long long>(B) * H > 65535)
+    return fail(DADATTN_E_UNSUPPORTED, "B*H=%lld exceeds 65535 per call", static_cast<long long>(B) * H);
+  if (D != 64)
+    return fail(DADATTN_E_UNSUPPORTED, "interleaved [B*S, H*D] activations are taken at head size 64 only (got %d)", D);
+  return flash_bwd_bf16_checked(dq, dk, dv, workspace, workspace_bytes, dout, out, lse, q, k, v, B * H, S, D,
+                                scale, rate, seed, offset, unit0, nullptr, H, stream);
 }

@@ -74,13 +74,13 @@ __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, const 
       ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
-// TMA store of one [128 rows][64 bf16] swizzled panel from shared memory; rows beyond the
-// tensor's extent are dropped.
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* smem_src, int x, int y,
-                                             int z) {
+// TMA store of one [128 rows][64 bf16] swizzled panel from shared memory to (x, row, head, batch)
+// of a tensor in either memory layout (UnitLayout); rows beyond the sequence are dropped.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* smem_src, int x, int y,
+                                             int z, int w) {
   asm volatile(
-      "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
-      ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+      "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
@@ -149,7 +149,7 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_dqw, const __grid_constant__ CUtensorMap map_dk,
                        const __grid_constant__ CUtensorMap map_dv, const float* __restrict__ lse,
                        const float* __restrict__ delta, int* __restrict__ item_counter, int BH, int S,
-                       int group_bh, float scale, float rate, PhiloxKey rng, int64_t unit0,
+                       int heads, int group_bh, float scale, float rate, PhiloxKey rng, int64_t unit0,
                        const uint32_t* __restrict__ mask_bits, int* __restrict__ status) {
   using L = FusedSmem;
   constexpr int D = kFD;
@@ -239,17 +239,18 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int kb = j & 1;
         if (ok && j >= 2) ok = mbar_wait(&bars->dkv_sent[kb], ((j >> 1) - 1) & 1, abort_flag);
         if (!ok) break;
+        const int ub = t.bh / heads, uh = t.bh - ub * heads;   // (batch, head) of the unit
         mbar_arrive_expect_tx(&bars->kv_full[kb], 2 * kFPanel);
-        tma_load_3d(smem + L::kK + kb * kFPanel, &map_k, &bars->kv_full[kb], 0, t.kt * kFT, t.bh);
-        tma_load_3d(smem + L::kV + kb * kFPanel, &map_v, &bars->kv_full[kb], 0, t.kt * kFT, t.bh);
+        tma_load_4d(smem + L::kK + kb * kFPanel, &map_k, &bars->kv_full[kb], 0, t.kt * kFT, uh, ub);
+        tma_load_4d(smem + L::kV + kb * kFPanel, &map_v, &bars->kv_full[kb], 0, t.kt * kFT, uh, ub);
         for (int i = 0; i < t.n_it; ++i, ++g) {
           const int s = g % kFStages, use = g / kFStages;
           if (use > 0 && !(ok = mbar_wait(&bars->qdo_empty[s], (use - 1) & 1, abort_flag))) break;
           const int q0 = (t.kt + i) * kFT;
           mbar_arrive_expect_tx(&bars->q_full[s], kFPanel);
-          tma_load_3d(smem + L::kQ + s * kFPanel, &map_q, &bars->q_full[s], 0, q0, t.bh);
+          tma_load_4d(smem + L::kQ + s * kFPanel, &map_q, &bars->q_full[s], 0, q0, uh, ub);
           mbar_arrive_expect_tx(&bars->do_full[s], kFPanel);
-          tma_load_3d(smem + L::kDO + s * kFPanel, &map_do, &bars->do_full[s], 0, q0, t.bh);
+          tma_load_4d(smem + L::kDO + s * kFPanel, &map_do, &bars->do_full[s], 0, q0, uh, ub);
         }
         cur = nxt;
         nxt = after;
@@ -377,8 +378,9 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // The next phase of dkv_staged[j & 1] belongs to item j + 2 and cannot complete
             // before this warp has handed back the staging buffer of item j's last tile.
             if (!(ok = mbar_wait(&bars->dkv_staged[j & 1], (j >> 1) & 1, abort_flag))) break;
-            tma_store_3d(&map_dk, smem + L::kK + (j & 1) * kFPanel, 0, t.kt * kFT, t.bh);
-            tma_store_3d(&map_dv, smem + L::kV + (j & 1) * kFPanel, 0, t.kt * kFT, t.bh);
+            const int ub = t.bh / heads, uh = t.bh - ub * heads;
+            tma_store_4d(&map_dk, smem + L::kK + (j & 1) * kFPanel, 0, t.kt * kFT, uh, ub);
+            tma_store_4d(&map_dv, smem + L::kV + (j & 1) * kFPanel, 0, t.kt * kFT, uh, ub);
             bulk_commit();
             bulk_wait_read1();
             mbar_arrive(&bars->dq_sent);
@@ -618,13 +620,15 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 // the kernel before this one in the stream (normally the forward pass), so it runs ahead of the
 // dependency wait and overlaps that kernel's tail. The only kernel that reads the workspace,
 // fused_convert_kernel, releases its dependents after its reads.
+template <bool INTERLEAVED>
 __global__ void fused_prepare_kernel(float* __restrict__ delta, float* __restrict__ dq_ws,
                                      int* __restrict__ item_counter,
                                      const __nv_bfloat16* __restrict__ dout,
-                                     const __nv_bfloat16* __restrict__ out, int64_t rows) {
+                                     const __nv_bfloat16* __restrict__ out, int64_t rows, int S,
+                                     UnitLayout lay) {
   constexpr int D = kFD, Lr = D / 8;  // 8 lanes per row
   const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int64_t r = t / Lr;
+  const int64_t r = t / Lr;   // row of the [BH, S] index space: delta and the workspace are heads-split
   const int c = static_cast<int>(t % Lr) * 8;
   if (r < rows) {
     float4* z = reinterpret_cast<float4*>(dq_ws + r * D + c);
@@ -636,8 +640,15 @@ __global__ void fused_prepare_kernel(float* __restrict__ delta, float* __restric
   pdl_launch_dependents();
   float sum = 0.f;
   if (r < rows) {
-    const uint4 a = *reinterpret_cast<const uint4*>(dout + r * D + c);
-    const uint4 b = *reinterpret_cast<const uint4*>(out + r * D + c);
+    // where row r = (unit, s) lies in dO and O: heads-split rows are simply consecutive
+    int64_t at = r * D + c;
+    if (INTERLEAVED) {
+      const int unit = static_cast<int>(r / S), srow = static_cast<int>(r - static_cast<int64_t>(unit) * S);
+      const int ub = unit / lay.heads, uh = unit - ub * lay.heads;
+      at = ub * lay.batch + uh * lay.head + srow * lay.row + c;
+    }
+    const uint4 a = *reinterpret_cast<const uint4*>(dout + at);
+    const uint4 b = *reinterpret_cast<const uint4*>(out + at);
     const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -652,8 +663,9 @@ __global__ void fused_prepare_kernel(float* __restrict__ delta, float* __restric
 
 // dQ workspace (fp32) -> dq (bf16). Dependents are released only after the workspace has been
 // read: the next backward call's prepare kernel clears it ahead of its own dependency wait.
+template <bool INTERLEAVED>
 __global__ void fused_convert_kernel(__nv_bfloat16* __restrict__ dq, const float* __restrict__ dq_ws,
-                                     int64_t n8) {
+                                     int64_t n8, int S, UnitLayout lay) {
   pdl_wait();
   const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
@@ -663,7 +675,18 @@ __global__ void fused_convert_kernel(__nv_bfloat16* __restrict__ dq, const float
   }
   // the loads have returned once their values are used; keep the trigger behind that use
   const uint4 w = make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
-  if (t < n8) *reinterpret_cast<uint4*>(dq + t * 8) = w;
+  if (t < n8) {
+    // workspace row r = (unit, s), 8 elements at column c; heads-split dq has the same order
+    int64_t at = t * 8;
+    if (INTERLEAVED) {
+      const int64_t r = t / (kFD / 8);
+      const int c = static_cast<int>(t - r * (kFD / 8)) * 8;
+      const int unit = static_cast<int>(r / S), srow = static_cast<int>(r - static_cast<int64_t>(unit) * S);
+      const int ub = unit / lay.heads, uh = unit - ub * lay.heads;
+      at = ub * lay.batch + uh * lay.head + srow * lay.row + c;
+    }
+    *reinterpret_cast<uint4*>(dq + at) = w;
+  }
   pdl_launch_dependents();
 }
 
@@ -709,20 +732,23 @@ size_t fused_bwd_workspace_bytes(int BH, int S) {
 int launch_bwd_fused_d64(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspace, const uint16_t* dout,
                          const uint16_t* out, const float* lse, const uint16_t* q, const uint16_t* k,
                          const uint16_t* v, int BH, int S, float scale, float rate, uint64_t seed,
-                         uint64_t offset, int64_t unit0, const uint32_t* mask_bits, cudaStream_t st) {
+                         uint64_t offset, int64_t unit0, const uint32_t* mask_bits, int heads,
+                         cudaStream_t st) {
   using BF = __nv_bfloat16;
+  // heads > 0: every bf16 tensor is the interleaved [B*S, heads*64] activation (BH = B * heads)
+  const UnitLayout lay = heads > 0 ? unit_layout(BH / heads, heads, S, kFD, true) : unit_layout(BH, 1, S, kFD, false);
   const size_t delta_bytes = (static_cast<size_t>(BH) * S * sizeof(float) + 255) / 256 * 256;
   const size_t dq_bytes = (static_cast<size_t>(BH) * S * kFD * sizeof(float) + 255) / 256 * 256;
   float* delta = static_cast<float*>(workspace);
   float* dq_ws = reinterpret_cast<float*>(static_cast<char*>(workspace) + delta_bytes);
   int* item_counter = reinterpret_cast<int*>(static_cast<char*>(workspace) + delta_bytes + dq_bytes);
   CUtensorMap mq, mk, mv, mdo, mws, mdk, mdv;
-  if (int rc = make_tensor_map_bf16(&mq, q, BH, S, kFD, kFT)) return rc;
-  if (int rc = make_tensor_map_bf16(&mk, k, BH, S, kFD, kFT)) return rc;
-  if (int rc = make_tensor_map_bf16(&mv, v, BH, S, kFD, kFT)) return rc;
-  if (int rc = make_tensor_map_bf16(&mdo, dout, BH, S, kFD, kFT)) return rc;
-  if (int rc = make_tensor_map_bf16(&mdk, dk, BH, S, kFD, kFT)) return rc;
-  if (int rc = make_tensor_map_bf16(&mdv, dv, BH, S, kFD, kFT)) return rc;
+  if (int rc = make_tensor_map_bf16_units(&mq, q, BH, S, kFD, kFT, lay)) return rc;
+  if (int rc = make_tensor_map_bf16_units(&mk, k, BH, S, kFD, kFT, lay)) return rc;
+  if (int rc = make_tensor_map_bf16_units(&mv, v, BH, S, kFD, kFT, lay)) return rc;
+  if (int rc = make_tensor_map_bf16_units(&mdo, dout, BH, S, kFD, kFT, lay)) return rc;
+  if (int rc = make_tensor_map_bf16_units(&mdk, dk, BH, S, kFD, kFT, lay)) return rc;
+  if (int rc = make_tensor_map_bf16_units(&mdv, dv, BH, S, kFD, kFT, lay)) return rc;
   if (int rc = make_dq_workspace_map(&mws, dq_ws, BH, S)) return rc;
   int* status = device_status_word();
   if (!status) return DADATTN_E_CUDA;
@@ -730,9 +756,10 @@ int launch_bwd_fused_d64(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspa
   const int64_t rows = static_cast<int64_t>(BH) * S;
   const int64_t prep_threads = rows * (kFD / 8);
   stage_event(0, st);
-  DAD_CUDA(launch_pdl(fused_prepare_kernel, dim3(static_cast<unsigned>((prep_threads + 255) / 256)),
+  DAD_CUDA(launch_pdl(heads > 0 ? fused_prepare_kernel<true> : fused_prepare_kernel<false>,
+                      dim3(static_cast<unsigned>((prep_threads + 255) / 256)),
                       dim3(256), 0, st, delta, dq_ws, item_counter, reinterpret_cast<const BF*>(dout),
-                      reinterpret_cast<const BF*>(out), rows));
+                      reinterpret_cast<const BF*>(out), rows, S, lay));
   stage_event(1, st);
   const PhiloxKey rng = make_philox(seed, offset);
   // One persistent CTA per SM; the CTAs draw (key tile, batch x head) items from a counter.
@@ -750,12 +777,13 @@ int launch_bwd_fused_d64(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspa
                          : flash_bwd_fused_kernel<0>;
   DAD_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FusedSmem::kBytes));
   DAD_CUDA(launch_pdl(kern, grid, dim3(kFThreads), FusedSmem::kBytes, st, mq, mk, mv, mdo, mws, mdk, mdv,
-                      lse, static_cast<const float*>(delta), item_counter, BH, S, group_bh, scale, rate,
+                      lse, static_cast<const float*>(delta), item_counter, BH, S, lay.heads, group_bh, scale, rate,
                       rng, unit0, mask_bits, status));
   stage_event(2, st);
   const int64_t n8 = rows * kFD / 8;
-  DAD_CUDA(launch_pdl(fused_convert_kernel, dim3(static_cast<unsigned>((n8 + 255) / 256)), dim3(256), 0,
-                      st, reinterpret_cast<BF*>(dq), static_cast<const float*>(dq_ws), n8));
+  DAD_CUDA(launch_pdl(heads > 0 ? fused_convert_kernel<true> : fused_convert_kernel<false>,
+                      dim3(static_cast<unsigned>((n8 + 255) / 256)), dim3(256), 0,
+                      st, reinterpret_cast<BF*>(dq), static_cast<const float*>(dq_ws), n8, S, lay));
   stage_event(3, st);
   return DADATTN_OK;
 }

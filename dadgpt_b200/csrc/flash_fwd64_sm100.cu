@@ -183,8 +183,9 @@ template <int DROP>
 __global__ void __launch_bounds__(kFwd64Threads, 1)
 flash_fwd64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
-                   float* __restrict__ lse, int BH, int S, float scale, float rate, PhiloxKey rng,
-                   int64_t unit0, const uint4* __restrict__ mask_bits, int* __restrict__ status) {
+                   float* __restrict__ lse, int BH, int S, UnitLayout lay, float scale, float rate,
+                   PhiloxKey rng, int64_t unit0, const uint4* __restrict__ mask_bits,
+                   int* __restrict__ status) {
   using L = F64Smem;
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kColS = 0, kColO = 256;   // S_X at kColS + 128 X, O_(X,h) at kColO + 64 (2 X + h)
@@ -249,18 +250,19 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const int qb = k & 1;
         // the Q buffer frees when the last score product of the item before last has completed
         if (k >= 2 && !mbar_wait(&bars->q_empty[qb], ((k >> 1) - 1) & 1, abort_flag)) break;
+        const int ub = it.bh / lay.heads, uh = it.bh - ub * lay.heads;   // (batch, head) of the unit
         mbar_arrive_expect_tx(&bars->q_full[qb], it.n_b ? 2 * kPanel : kPanel);
-        tma_load_3d(smem + L::kQ + (qb * 2 + 0) * kPanel, &map_q, &bars->q_full[qb], 0, it.qa * kT, it.bh);
+        tma_load_4d(smem + L::kQ + (qb * 2 + 0) * kPanel, &map_q, &bars->q_full[qb], 0, it.qa * kT, uh, ub);
         if (it.n_b)
-          tma_load_3d(smem + L::kQ + (qb * 2 + 1) * kPanel, &map_q, &bars->q_full[qb], 0,
-                      (it.qa + 1) * kT, it.bh);
+          tma_load_4d(smem + L::kQ + (qb * 2 + 1) * kPanel, &map_q, &bars->q_full[qb], 0,
+                      (it.qa + 1) * kT, uh, ub);
         for (int j = 0; j < it.n_kv; ++j, ++g) {
           const int s = g % kKvStages, use = g / kKvStages;
           if (use > 0 && !(ok = mbar_wait(&bars->kv_empty[s], (use - 1) & 1, abort_flag))) break;
           mbar_arrive_expect_tx(&bars->k_full[s], kPanel);
-          tma_load_3d(smem + L::kK + s * kPanel, &map_k, &bars->k_full[s], 0, j * kT, it.bh);
+          tma_load_4d(smem + L::kK + s * kPanel, &map_k, &bars->k_full[s], 0, j * kT, uh, ub);
           mbar_arrive_expect_tx(&bars->v_full[s], kPanel);
-          tma_load_3d(smem + L::kV + s * kPanel, &map_v, &bars->v_full[s], 0, j * kT, it.bh);
+          tma_load_4d(smem + L::kV + s * kPanel, &map_v, &bars->v_full[s], 0, j * kT, uh, ub);
         }
       }
     }
@@ -522,7 +524,8 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const float w1 = (s1.x == -INFINITY) ? 0.f : ex2(s1.x - m_tot);
       const float l_tot = s0.y * w0 + s1.y * w1;
       const float f0 = w0 / l_tot, f1 = w1 / l_tot;
-      __nv_bfloat16* dst = out + (static_cast<size_t>(it.bh) * S + r) * kHD + half * 32;
+      const int ub = it.bh / lay.heads, uh = it.bh - ub * lay.heads;
+      __nv_bfloat16* dst = out + ub * lay.batch + uh * lay.head + r * lay.row + half * 32;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {   // 16 output columns at a time
         uint32_t oa[16], ob[16];
@@ -565,12 +568,12 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
 template <int DROP>
 int launch_fwd64(uint16_t* out, float* lse, const uint16_t* q, const uint16_t* k, const uint16_t* v,
-                 int BH, int S, float scale, float rate, uint64_t seed, uint64_t offset, int64_t unit0,
-                 const uint32_t* mask_bits, cudaStream_t st) {
+                 int BH, int S, const UnitLayout& lay, float scale, float rate, uint64_t seed,
+                 uint64_t offset, int64_t unit0, const uint32_t* mask_bits, cudaStream_t st) {
   CUtensorMap mq, mk, mv;
-  if (int rc = make_tensor_map_bf16(&mq, q, BH, S, kHD, kT)) return rc;
-  if (int rc = make_tensor_map_bf16(&mk, k, BH, S, kHD, kT)) return rc;
-  if (int rc = make_tensor_map_bf16(&mv, v, BH, S, kHD, kT)) return rc;
+  if (int rc = make_tensor_map_bf16_units(&mq, q, BH, S, kHD, kT, lay)) return rc;
+  if (int rc = make_tensor_map_bf16_units(&mk, k, BH, S, kHD, kT, lay)) return rc;
+  if (int rc = make_tensor_map_bf16_units(&mv, v, BH, S, kHD, kT, lay)) return rc;
   int* status = device_status_word();
   if (!status) return DADATTN_E_CUDA;
   int dev = 0, sms = 0;
@@ -583,7 +586,7 @@ int launch_fwd64(uint16_t* out, float* lse, const uint16_t* q, const uint16_t* k
   DAD_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, F64Smem::kBytes));
   dim3 grid(static_cast<unsigned>(n_items < sms ? n_items : sms));
   DAD_CUDA(launch_pdl(kern, grid, dim3(kFwd64Threads), F64Smem::kBytes, st, mq, mk, mv,
-                      reinterpret_cast<__nv_bfloat16*>(out), lse, BH, S, scale, rate,
+                      reinterpret_cast<__nv_bfloat16*>(out), lse, BH, S, lay, scale, rate,
                       make_philox(seed, offset), unit0, reinterpret_cast<const uint4*>(mask_bits), status));
   return DADATTN_OK;
 }
@@ -591,15 +594,17 @@ int launch_fwd64(uint16_t* out, float* lse, const uint16_t* q, const uint16_t* k
 }  // namespace
 
 // Forward at head size 64. mask_bits != nullptr: keep bits from dadattn_dropout_mask_bits;
-// otherwise rate > 0 draws the Philox mask inside the kernel.
+// otherwise rate > 0 draws the Philox mask inside the kernel. heads > 0: q, k, v, out are the
+// interleaved [B*S, heads*64] activations (BH = B * heads units); heads = 0: heads-split [BH,S,64].
 int launch_fwd_bf16_d64(uint16_t* out, float* lse, const uint16_t* q, const uint16_t* k, const uint16_t* v,
                         int BH, int S, float scale, float rate, uint64_t seed, uint64_t offset,
-                        int64_t unit0, const uint32_t* mask_bits, cudaStream_t st) {
+                        int64_t unit0, const uint32_t* mask_bits, int heads, cudaStream_t st) {
+  const UnitLayout lay = heads > 0 ? unit_layout(BH / heads, heads, S, kHD, true) : unit_layout(BH, 1, S, kHD, false);
   if (rate > 0.f && mask_bits)
-    return launch_fwd64<2>(out, lse, q, k, v, BH, S, scale, rate, 0, 0, 0, mask_bits, st);
+    return launch_fwd64<2>(out, lse, q, k, v, BH, S, lay, scale, rate, 0, 0, 0, mask_bits, st);
   if (rate > 0.f)
-    return launch_fwd64<1>(out, lse, q, k, v, BH, S, scale, rate, seed, offset, unit0, nullptr, st);
-  return launch_fwd64<0>(out, lse, q, k, v, BH, S, scale, 0.f, 0, 0, 0, nullptr, st);
+    return launch_fwd64<1>(out, lse, q, k, v, BH, S, lay, scale, rate, seed, offset, unit0, nullptr, st);
+  return launch_fwd64<0>(out, lse, q, k, v, BH, S, lay, scale, 0.f, 0, 0, 0, nullptr, st);
 }
 
 }  // namespace dadattn

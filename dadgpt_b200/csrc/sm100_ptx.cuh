@@ -108,6 +108,18 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// 4-D form: (x, row, head, batch). The bf16 kernels address a (batch, head) unit this way so
+// that one code path serves both memory layouts (see UnitLayout below).
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                            int x, int y, int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x),
+      "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+
 // ---- tensor memory ----------------------------------------------------------------------------
 // Whole-warp calls. ncols: power of two in [32, 512].
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {
@@ -245,5 +257,25 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // 3-D map over a contiguous bf16 [BH, S, D] tensor with a box of 64 x `box_rows` x 1 elements
 // and 128-byte swizzle; out-of-range rows read as zero. Returns 0 or a DADATTN_E_* code.
 int make_tensor_map_bf16(CUtensorMap* map, const void* base, int BH, int S, int D, int box_rows);
+
+// Where the rows of a (batch, head) unit lie. Heads-split (the reference's q_heads / k_heads /
+// v_heads after gpu_split_heads, cuda/gpu_ops.cu:428-474): [B*H, S, D] contiguous. Interleaved
+// (the reference's activations BEFORE the split, [B*S, H*D], src/model.cpp:372-387): row s of
+// unit (b, h) starts at ((b S + s) H + h) D. Both are a 4-D tensor (d, s, h, b) with different
+// strides, so one tensor map and one (x, row, h, b) coordinate serve both; the heads-split form is
+// used with heads = 1, batch = B*H.
+struct UnitLayout {
+  int heads;            // H of the (h, b) split of a unit index: b = unit / heads, h = unit % heads
+  int64_t row, head, batch;   // element strides of a query / key row, a head, a batch entry
+};
+inline UnitLayout unit_layout(int B, int H, int S, int D, bool interleaved) {
+  if (!interleaved) return UnitLayout{1, D, 0, static_cast<int64_t>(S) * D};  // unit = b H + h, heads folded
+  return UnitLayout{H, static_cast<int64_t>(H) * D, D, static_cast<int64_t>(S) * H * D};
+}
+// 4-D map (d, s, h, b) over a bf16 tensor in either layout; box 64 x box_rows x 1 x 1, 128-byte
+// swizzle; rows beyond S read as zero and are dropped on stores. For the heads-split layout
+// pass units = B*H: the map is then (D, S, 1, B*H).
+int make_tensor_map_bf16_units(CUtensorMap* map, const void* base, int units, int S, int D, int box_rows,
+                               const UnitLayout& lay);
 
 }  // namespace dadattn

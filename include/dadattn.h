@@ -148,6 +148,26 @@ int dadattn_flash_bwd_bf16_masked(uint16_t* dq, uint16_t* dk, uint16_t* dv, void
                                   const uint16_t* v, int BH, int S, int D, float scale, float rate,
                                   const uint32_t* mask_bits, dadattn_stream_t stream);
 
+/* The same two calls on the activations BEFORE the reference's head split: q, k, v, out, dout,
+ * dq, dk, dv are [B*S, H*D] row-major (row = b S + s, column = h D + d), exactly what the
+ * projections write and read (reference src/model.cpp:372-387,423,564,619-624), so the three
+ * gpu_split_heads copies before and the gpu_merge_heads copy after the forward, and the one split
+ * and three merges around the backward (cuda/gpu_ops.cu:428-474), are not needed: the kernels
+ * address the rows of a (batch, head) unit through strided tensor maps. lse stays [B*H, S];
+ * results equal split -> dadattn_flash_*_bf16 -> merge. Head size 64; the backward must be the
+ * single-pass one (the default). workspace as for dadattn_flash_bwd_bf16 with BH = B*H. No
+ * counterpart signature in the reference. */
+int dadattn_flash_fwd_bf16_strided(uint16_t* out, float* lse, const uint16_t* q, const uint16_t* k,
+                                   const uint16_t* v, int B, int H, int S, int D, float scale,
+                                   float rate, uint64_t seed, uint64_t offset, int64_t unit0,
+                                   dadattn_stream_t stream);
+int dadattn_flash_bwd_bf16_strided(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspace,
+                                   size_t workspace_bytes, const uint16_t* dout, const uint16_t* out,
+                                   const float* lse, const uint16_t* q, const uint16_t* k,
+                                   const uint16_t* v, int B, int H, int S, int D, float scale,
+                                   float rate, uint64_t seed, uint64_t offset, int64_t unit0,
+                                   dadattn_stream_t stream);
+
 /* By default the backward is a single-pass kernel (one per head size) that forms the
  * probabilities once and adds each key tile's dQ contribution into an fp32 accumulator in the
  * workspace (TMA / bulk reduce-add): about 1.4-2x as fast as recomputing them, but the order of

@@ -78,8 +78,14 @@ def test_gpuops_shim_defines_the_reference_symbols():
         ref = subprocess.run(["nm", "-D", "--defined-only", ref_obj], capture_output=True,
                              text=True, check=True).stdout
         for line in out.splitlines():
-            if "gpu_flash_attention" in line:
-                assert line.split()[-1] in ref
+            name = line.split()[-1]
+            # the three reference symbols; the *_dropout additions have no counterpart there
+            if "gpu_flash_attention" in name and "dropout" not in name:
+                assert name in ref
+    # additions declared in include/dadattn_gpu_ops.hpp
+    for sym in ("gpu_flash_attention_forward_dropout", "gpu_flash_attention_backward_dropout",
+                "gpu_decode_attention"):
+        assert sym in out, sym
 
 
 def test_python_mirror_rejects_cpu_tensors():
