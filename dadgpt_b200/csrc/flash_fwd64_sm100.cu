@@ -10,17 +10,23 @@
 //     (batch, head); both use the same K/V tiles from one shared-memory ring and each has its
 //     own softmax group. While group A computes exponentials the tensor pipe runs B's products
 //     and vice versa;
-//   * a group is 256 threads, TWO per query row: one takes key columns 0-63 of every tile, the
-//     other columns 64-127. Each half keeps its OWN running max / sum and its OWN output
+//   * a K/V tile is worked through in two sub-steps of 64 keys, and every group has TWO score
+//     buffers of 64 columns in tensor memory: while the group's threads work on the scores of
+//     one sub-step, the product for the next one is already running into the other buffer, so in
+//     steady state nobody waits for the tensor pipe and the tensor pipe waits for nobody;
+//   * a group is 256 threads, TWO per query row: one takes key columns 0-31 of every sub-step,
+//     the other columns 32-63. Each keeps its OWN running max / sum and its OWN output
 //     accumulator in tensor memory (split-K inside the CTA), so the two threads of a row never
-//     talk inside the loop; the halves are merged once per item, in the epilogue. Sixteen
-//     softmax warps, four per scheduler, are what hides the tensor-memory and exp2 latencies;
-//   * the probabilities never touch shared memory: a thread reads its 64 scores from tensor
+//     talk inside the loop; they are merged once per item, in the epilogue. Sixteen softmax
+//     warps, four per scheduler, are what hides the tensor-memory and exp2 latencies;
+//   * the probabilities never touch shared memory: a thread reads its 32 scores from tensor
 //     memory once, keeps them in registers for the max and the exponentials, and writes P back
 //     as packed bf16 over the first half of the same columns, from where the P V product takes
 //     it as its A operand;
 //   * scale-and-subtract and the row sums run as packed two-float instructions (fma.rn.f32x2,
-//     add.rn.f32x2) and the row max as three-input max: about 3 issue slots per score;
+//     add.rn.f32x2), the row max as three-input max, and one pair of exponentials in four as a
+//     cubic on the FMA pipe (a bf16x2 exp2 on the special-function unit was tried: no faster, and
+//     it cost a digit of lse): the softmax is bound by instruction issue, not by any one unit;
 //   * CTAs are persistent: barriers, tensor memory and descriptors are set up once, items are
 //     dealt out heaviest first in a fixed serpentine order (no global counter to reset), the
 //     next item's Q tiles and first K/V tiles are in flight while the current one finishes, and
@@ -30,10 +36,10 @@
 //   warp 1        MMA issuer of group A, owner of the tensor-memory allocation
 //   warp 18       MMA issuer of group B (one issuing thread per group: a group's products are
 //                 issued the moment its probabilities are ready, whatever the other group does)
-//   warps 2-9     softmax group A (2-5: key columns 0-63, 6-9: 64-127)
+//   warps 2-9     softmax group A (2-5: key columns 0-31 of a sub-step, 6-9: 32-63)
 //   warps 10-17   softmax group B likewise
-// Tensor memory: S_A [0,128) S_B [128,256); O of (group X, half h) at 256 + 64 (2 X + h);
-// P of half h aliases the first 32 columns of its half of S_X.
+// Tensor memory: score buffer b of group X at 128 X + 64 b; O of (group X, half h) at
+// 256 + 64 (2 X + h); P of half h aliases the first 16 columns of its 32 columns of the buffer.
 //
 // Every mbarrier wait is bounded (sm100_ptx.cuh); on expiry the CTA raises its abort flag, all
 // roles fall through to the common exit, tensor memory is freed and DADATTN_E_TIMEOUT is left in
@@ -72,7 +78,7 @@ struct F64Smem {
 struct F64Bars {
   uint64_t q_full[2], q_empty[2];
   uint64_t k_full[kKvStages], v_full[kKvStages], kv_empty[kKvStages];
-  uint64_t s_full[2], p_full[2], o_done[2][2], o_free[2], stat_full[2];   // first index: group A / B
+  uint64_t s_full[2][2], p_full[2][2], o_done[2][2], o_free[2], stat_full[2];   // [group][buffer]
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -188,7 +194,7 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                    int* __restrict__ status) {
   using L = F64Smem;
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kColS = 0, kColO = 256;   // S_X at kColS + 128 X, O_(X,h) at kColO + 64 (2 X + h)
+  constexpr uint32_t kColS = 0, kColO = 256;   // score buffer (X,b) at 128 X + 64 b, O_(X,h) at kColO + 64 (2 X + h)
 
   extern __shared__ __align__(1024) uint8_t smem[];
   F64Bars* bars = reinterpret_cast<F64Bars*>(smem + L::kBars);
@@ -208,8 +214,10 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars->q_full[b], 1);
       mbar_init(&bars->q_empty[b], 2);              // one arrival per issuer
-      mbar_init(&bars->s_full[b], 1);
-      mbar_init(&bars->p_full[b], 2 * kHalfThreads);
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(&bars->s_full[b][i], 1);
+        mbar_init(&bars->p_full[b][i], 2 * kHalfThreads);
+      }
       mbar_init(&bars->o_done[b][0], 1);
       mbar_init(&bars->o_done[b][1], 1);
       mbar_init(&bars->o_free[b], 2 * kHalfThreads);
@@ -268,47 +276,49 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
   } else if (warp == 1 || warp == 18) {
     // ------------------------------ MMA issuers ------------------------------
-    // One issuing thread per group. Issuer X walks the K/V ring tiles of all items in order and,
-    // per tile g, issues O_X += P_X V(g) and then S_X = Q_X K(g+1)^T (the next tile's scores, also
-    // across an item boundary). A ring stage and a Q buffer are released by both issuers: each
-    // commits (or, where its group has nothing to do with the tile, simply arrives) once.
+    // One issuing thread per group. Issuer X walks the K/V ring tiles of all items in order, each
+    // tile as two sub-steps of 64 keys. For sub-step (g, c) it issues O_X += P_X V(g, c) and then
+    // S_X = Q_X K(g+1, c)^T, the scores two sub-steps ahead, into the buffer that P_X(g, c) has
+    // just left (also across an item boundary). A ring stage and a Q buffer are released by both
+    // issuers: each commits (or, where its group has nothing to do with the tile, arrives) once.
     if (elect_one()) {
       const int X = (warp == 1) ? 0 : 1;
-      constexpr uint32_t idesc_s = make_idesc_bf16(kT, kT, 0, 0);    // Q, K: K-major
+      constexpr uint32_t idesc_s = make_idesc_bf16(kT, 64, 0, 0);    // Q, K: K-major; 64 keys
       constexpr uint32_t idesc_o = make_idesc_bf16(kT, kHD, 0, 1);   // P from TMEM, V MN-major
       const SmemDescBase q_desc0 = make_desc_base_sw128(smem_u32(smem + L::kQ), 0);
       const SmemDescBase k_desc0 = make_desc_base_sw128(smem_u32(smem + L::kK), 0);
       const SmemDescBase v_desc0 = make_desc_base_sw128(smem_u32(smem + L::kV), 0);
       const uint32_t tSx = tmem + kColS + X * 128, tOx = tmem + kColO + X * 2 * kHD;
-      int n_pv = 0;      // P V products of this group issued so far
+      int n_pv = 0;      // sub-steps of this group whose P V products have been issued
       int n_done = 0;    // items finished so far in which the group took part
       bool ok = true;
 
-      // S_X = Q_X K^T for K/V ring tile g of the item in Q buffer qb
-      auto issue_s = [&](int qb, int g) {
+      // S_X = Q_X K^T for the 64 keys of sub-step c of K/V ring tile g, item in Q buffer qb; the
+      // group's sub-steps alternate between its two score buffers, and c is the buffer
+      auto issue_s = [&](int qb, int g, int c) {
         const SmemDescBase qd{q_desc0.lo + (qb * 2 + X) * (kPanel >> 4), q_desc0.hi};
         const SmemDescBase kd{k_desc0.lo + (g % kKvStages) * (kPanel >> 4), k_desc0.hi};
 #pragma unroll
         for (int kk = 0; kk < kHD / 16; ++kk)
-          mma_ss(tSx, desc_at(qd, kk * 32), desc_at(kd, kk * 32), idesc_s, kk > 0 ? 1u : 0u);
-        mma_commit(&bars->s_full[X]);
+          mma_ss(tSx + c * 64, desc_at(qd, kk * 32), desc_at(kd, c * 8192 + kk * 32), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(&bars->s_full[X][c]);
       };
-      // O_(X,h) (+)= P_(X,h) V[64 h .. 64 h + 63] for ring tile g, both halves. P of half h sits
-      // in the first 32 columns of its half of S_X, 16 keys (8 columns of packed bf16 pairs) per
-      // MMA; V is MN-major, 16 keys = 2048 bytes further down.
-      auto issue_pv = [&](int g, bool first_of_item) -> bool {
+      // O_(X,h) (+)= P_(X,h) V[keys 64 c + 32 h .. + 31] of ring tile g, both halves. P of half h
+      // sits in the first 16 columns of its 32 columns of buffer c, 16 keys (8 columns of packed
+      // bf16 pairs) per MMA; V is MN-major, 16 keys = 2048 bytes further down.
+      auto issue_pv = [&](int g, int c, bool first_of_item) -> bool {
         // the epilogue of the group's previous item must have read O_X before it is overwritten
         if (first_of_item && n_done > 0 && !mbar_wait(&bars->o_free[X], (n_done - 1) & 1, abort_flag))
           return false;
-        if (!mbar_wait(&bars->p_full[X], n_pv & 1, abort_flag)) return false;
+        if (!mbar_wait(&bars->p_full[X][c], (n_pv >> 1) & 1, abort_flag)) return false;
         tc_fence_after_sync();
         const SmemDescBase vd{v_desc0.lo + (g % kKvStages) * (kPanel >> 4), v_desc0.hi};
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            mma_ts(tOx + h * kHD, tSx + h * 64 + kk * 8, desc_at(vd, (h * 4 + kk) * 2048), idesc_o,
-                   (!first_of_item || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < 2; ++kk)
+            mma_ts(tOx + h * kHD, tSx + c * 64 + h * 32 + kk * 8, desc_at(vd, (c * 4 + h * 2 + kk) * 2048),
+                   idesc_o, (!first_of_item || kk > 0) ? 1u : 0u);
         }
         mma_commit(&bars->o_done[X][n_pv & 1]);
         ++n_pv;
@@ -323,8 +333,11 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         ok = mbar_wait(&bars->q_full[0], 0, abort_flag) && mbar_wait(&bars->k_full[0], 0, abort_flag);
         if (ok) {
           tc_fence_after_sync();
-          if (n_of(cur) > 0) issue_s(0, 0);
-          if (n_of(cur) <= 1) {   // the item's only (or no) score product of this group
+          if (n_of(cur) > 0) {
+            issue_s(0, 0, 0);
+            issue_s(0, 0, 1);
+          }
+          if (n_of(cur) <= 1) {   // the item's only (or no) score products of this group
             if (n_of(cur) == 1) mma_commit(&bars->q_empty[0]); else mbar_arrive(&bars->q_empty[0]);
           }
         }
@@ -344,25 +357,34 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           // ahead and arrive twice within one phase of a release barrier.
           bool issued = false;
           ok = mbar_wait(&bars->v_full[s], (g / kKvStages) & 1, abort_flag);
-          if (ok && j < n_x) {
-            ok = issue_pv(g, j == 0);
-            issued = ok;
-          }
-          if (ok && have_next) {
-            const int n_next = n_of(ni);
-            if (last) ok = mbar_wait(&bars->q_full[nqb], ((k + 1) >> 1) & 1, abort_flag);
-            if (ok && nj < n_next) {
-              ok = mbar_wait(&bars->k_full[(g + 1) % kKvStages], ((g + 1) / kKvStages) & 1, abort_flag);
-              if (ok) {
-                tc_fence_after_sync();
-                issue_s(nqb, g + 1);
-                issued = true;
-                if (nj + 1 == n_next) mma_commit(&bars->q_empty[nqb]);   // the item's last scores of this group
-              }
-            } else if (ok && nj == 0) {
-              // the next item has no tile for this group: hand its Q buffer back
-              mbar_arrive(&bars->q_empty[nqb]);
+          const int n_next = have_next ? n_of(ni) : 0;
+          const bool s_next = have_next && nj < n_next;   // the group has scores to form in the next tile
+          bool next_ready = false;
+#pragma unroll
+          for (int c = 0; c < 2 && ok; ++c) {
+            if (j < n_x) {
+              ok = issue_pv(g, c, j == 0 && c == 0);
+              issued = ok;
             }
+            if (ok && s_next) {
+              if (!next_ready) {
+                if (last) ok = mbar_wait(&bars->q_full[nqb], ((k + 1) >> 1) & 1, abort_flag);
+                ok = ok && mbar_wait(&bars->k_full[(g + 1) % kKvStages], ((g + 1) / kKvStages) & 1, abort_flag);
+                if (ok) tc_fence_after_sync();
+                next_ready = true;
+              }
+              if (ok) {
+                issue_s(nqb, g + 1, c);
+                issued = true;
+                // the item's last scores of this group
+                if (c == 1 && nj + 1 == n_next) mma_commit(&bars->q_empty[nqb]);
+              }
+            }
+          }
+          if (ok && have_next && !s_next && nj == 0) {
+            // the next item has no tile for this group: hand its Q buffer back (once it is loaded)
+            if (last) ok = mbar_wait(&bars->q_full[nqb], ((k + 1) >> 1) & 1, abort_flag);
+            if (ok) mbar_arrive(&bars->q_empty[nqb]);
           }
           // this issuer's share of the stage's release: after every product of its that reads it
           if (ok) {
@@ -377,14 +399,14 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   } else {
     // ------------------------------ softmax groups ------------------------------
     const int X = (warp - 2) / 8;         // 0: group A (first tile of the pair), 1: group B (warps 2-17)
-    const int half = ((warp - 2) / 4) & 1;  // which 64 key columns of every tile
+    const int half = ((warp - 2) / 4) & 1;  // which 32 key columns of every 64-key sub-step
     const int quad = warp % 4;            // TMEM lane quadrant this warp may touch
     const int row = quad * 32 + lane;     // row within the tile = TMEM lane
     const uint32_t tlane = tmem + (static_cast<uint32_t>(quad * 32) << 16);
-    const uint32_t tS = tlane + kColS + X * 128 + half * 64;
+    const uint32_t tS0 = tlane + kColS + X * 128 + half * 32;   // this thread's columns of buffer 0
     const float scale_log2 = scale * kLog2e;
     const float keep_scale = DROP ? 1.0f / (1.0f - rate) : 1.0f;
-    int t = 0;        // score tiles this group has processed so far, over all items
+    int t = 0;        // 64-key sub-steps this group has processed so far, over all items
     int n_item = 0;   // items this group has taken part in
     bool ok = true;
 
@@ -394,116 +416,107 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const int n_x = X ? it.n_b : it.n_a;
       if (n_x == 0) continue;               // the pair's second tile lies beyond the sequence
       const int qt = it.qa + X;
-      const int limit = row - half * 64;    // diagonal tile: column i of this half visible iff i <= limit
       float m = -INFINITY;                  // running max of the scaled scores, log2 units
       float2 l2 = make_float2(0.f, 0.f);    // running sum, two interleaved partial sums
-      uint2 keep = make_uint2(~0u, ~0u), keep_next = keep;
-      const uint2* bits2 = reinterpret_cast<const uint2*>(mask_bits);
-      if (DROP == 2) keep_next = __ldg(bits2 + mask_bits_record(it.bh, qt, 0, row, n_tiles) * 2 + half);
+      const uint32_t* bits1 = reinterpret_cast<const uint32_t*>(mask_bits);
+      uint32_t keep = ~0u, keep_next = ~0u;
+      if (DROP == 2) keep_next = __ldg(bits1 + mask_bits_record(it.bh, qt, 0, row, n_tiles) * 4 + half);
 
-      for (int j = 0; j < n_x; ++j, ++t) {
+      for (int v = 0; v < 2 * n_x; ++v, ++t) {
+        const int j = v >> 1, c = v & 1;    // K/V tile and its sub-step; c is also the score buffer
         if (DROP == 2) {
-          keep = keep_next;   // fetched a tile ahead: its latency hides behind this tile's work
-          if (j + 1 < n_x)
-            keep_next = __ldg(bits2 + mask_bits_record(it.bh, qt, j + 1, row, n_tiles) * 2 + half);
+          keep = keep_next;   // fetched a sub-step ahead: its latency hides behind this one's work
+          if (v + 1 < 2 * n_x)
+            keep_next = __ldg(bits1 + mask_bits_record(it.bh, qt, (v + 1) >> 1, row, n_tiles) * 4 +
+                              ((v + 1) & 1) * 2 + half);
         }
-        if (!(ok = mbar_wait(&bars->s_full[X], t & 1, abort_flag))) break;
+        if (!(ok = mbar_wait(&bars->s_full[X][c], (t >> 1) & 1, abort_flag))) break;
         tc_fence_after_sync();
+        const uint32_t tS = tS0 + c * 64;
         const bool diagonal = (j == n_x - 1);
+        const int limit = row - c * 64 - half * 32;   // diagonal tile: column i visible iff i <= limit
 
-        // ---- the thread's 64 scores: read once, kept in registers for the max and the
+        // ---- the thread's 32 scores: read once, kept in registers for the max and the
         // exponentials ----
-        uint32_t xa[32], xb[32];
+        uint32_t xa[32];
         auto load_scores = [&]() {
           tmem_ld32(tS, xa);
-          tmem_ld32(tS + 32, xb);
           tmem_wait_ld();
           if (diagonal) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
+            for (int i = 0; i < 32; ++i)
               if (i > limit) xa[i] = 0xff800000u;  // -inf
-              if (32 + i > limit) xb[i] = 0xff800000u;
-            }
           }
         };
         load_scores();
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
+        for (int i = 0; i < 32; i += 4) {
           mx0 = fmax3(mx0, __uint_as_float(xa[i]), __uint_as_float(xa[i + 1]));
-          mx1 = fmax3(mx1, __uint_as_float(xb[i]), __uint_as_float(xb[i + 1]));
+          mx1 = fmax3(mx1, __uint_as_float(xa[i + 2]), __uint_as_float(xa[i + 3]));
         }
         const float mx = fmaxf(mx0, mx1) * scale_log2;   // scale > 0 commutes with max
 
         // ---- lazy rescale: O and the sum move to a new max only when it grew by 2^8 ----
-        if (j == 0) {
+        if (v == 0) {
           m = mx;  // O is first written by an MMA that does not accumulate: nothing to rescale
         } else if (__any_sync(0xffffffffu, mx > m + kRescaleAt)) {
-          // P V of this half's previous tile must have completed before O is touched
+          // P V of this group's previous sub-step must have completed before O is touched
           if (!(ok = mbar_wait(&bars->o_done[X][(t - 1) & 1], ((t - 1) >> 1) & 1, abort_flag))) break;
           tc_fence_after_sync();
           const float m_new = fmaxf(m, mx);
           // m = -inf: nothing but zeros has been accumulated so far (every earlier column masked)
           const float corr = (m == -INFINITY) ? 0.f : ex2(m - m_new);
 #pragma unroll 1
-          for (int c = 0; c < kHD / 32; ++c) {
+          for (int cc = 0; cc < kHD / 32; ++cc) {
             uint32_t o[32];
-            tmem_ld32(tlane + kColO + (X * 2 + half) * kHD + c * 32, o);
+            tmem_ld32(tlane + kColO + (X * 2 + half) * kHD + cc * 32, o);
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-            tmem_st32(tlane + kColO + (X * 2 + half) * kHD + c * 32, o);
+            tmem_st32(tlane + kColO + (X * 2 + half) * kHD + cc * 32, o);
           }
           tmem_wait_st();
           l2 = fmul2(l2, make_float2(corr, corr));
           m = m_new;
-          // read the scores again rather than keep 64 registers alive across this rare path
+          // read the scores again rather than keep them alive across this rare path
           load_scores();
         }
 
         // ---- p = exp2(s * scale * log2e - m); P goes back to tensor memory as packed bf16
-        // pairs over the first 32 of this half's columns. A half-row with no visible key yet has
+        // pairs over the first 16 of this thread's columns. A half-row with no visible key yet has
         // m = -inf: its scores are all -inf and must give p = 0, not exp2(nan). ----
         const float neg_m = (m == -INFINITY) ? 0.f : -m;
         const float2 sl = make_float2(scale_log2, scale_log2), nm = make_float2(neg_m, neg_m);
-        float2 la = make_float2(0.f, 0.f), lb = la;   // this tile's sums, two independent chains
-        auto exps = [&](const uint32_t (&x)[32], uint32_t (&dst)[16], int c0, uint32_t bits) {
+        float2 la = make_float2(0.f, 0.f), lb = la;   // this sub-step's sums, two independent chains
+        uint32_t pk[16];
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float2 e = ffma2(make_float2(__uint_as_float(x[i]), __uint_as_float(x[i + 1])), sl, nm);
-            float2 p;
-            if ((i & 7) == 6) {   // one pair in four on the FMA pipe
-              p = ex2_poly2(e);
-            } else {
-              p.x = ex2(e.x);
-              p.y = ex2(e.y);
-            }
-            if (i & 2) lb = fadd2(lb, p); else la = fadd2(la, p);
-            if (DROP == 1) {
-              const uint64_t idx = (static_cast<uint64_t>(unit0 + it.bh) * S + qt * kT + row) * S + j * kT + c0 + i;
-              p.x = (p.x != 0.f && philox_keep(rng, idx, rate)) ? p.x * keep_scale : 0.f;
-              p.y = (p.y != 0.f && philox_keep(rng, idx + 1, rate)) ? p.y * keep_scale : 0.f;
-            } else if (DROP == 2) {
-              p.x = ((bits >> i) & 1u) ? p.x * keep_scale : 0.f;
-              p.y = ((bits >> (i + 1)) & 1u) ? p.y * keep_scale : 0.f;
-            }
-            dst[i / 2] = pack_bf16(p.x, p.y);
+        for (int i = 0; i < 32; i += 2) {
+          const float2 e = ffma2(make_float2(__uint_as_float(xa[i]), __uint_as_float(xa[i + 1])), sl, nm);
+          float2 p;
+          if ((i & 7) == 6) {   // one pair in four on the FMA pipe
+            p = ex2_poly2(e);
+          } else {
+            p.x = ex2(e.x);
+            p.y = ex2(e.y);
           }
-        };
-        {
-          uint32_t pk[16];
-          exps(xa, pk, half * 64, keep.x);
-          tmem_st16(tS, pk);          // P of this half's keys 0..31 -> its columns 0..15
+          if (i & 2) lb = fadd2(lb, p); else la = fadd2(la, p);
+          if (DROP == 1) {
+            const uint64_t idx = (static_cast<uint64_t>(unit0 + it.bh) * S + qt * kT + row) * S + j * kT +
+                                 c * 64 + half * 32 + i;
+            p.x = (p.x != 0.f && philox_keep(rng, idx, rate)) ? p.x * keep_scale : 0.f;
+            p.y = (p.y != 0.f && philox_keep(rng, idx + 1, rate)) ? p.y * keep_scale : 0.f;
+          } else if (DROP == 2) {
+            p.x = ((keep >> i) & 1u) ? p.x * keep_scale : 0.f;
+            p.y = ((keep >> (i + 1)) & 1u) ? p.y * keep_scale : 0.f;
+          }
+          pk[i / 2] = pack_bf16(p.x, p.y);
         }
-        {
-          uint32_t pk[16];
-          exps(xb, pk, half * 64 + 32, keep.y);
-          tmem_st16(tS + 16, pk);     // keys 32..63 -> columns 16..31
-        }
+        tmem_st16(tS, pk);          // P of this thread's 32 keys -> its first 16 columns
         l2 = fadd2(l2, fadd2(la, lb));
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(&bars->p_full[X]);
+        mbar_arrive(&bars->p_full[X][c]);
       }
       if (!ok) break;
 
