@@ -20,6 +20,7 @@ from .attention import (  # noqa: F401
     gpu_flash_attention_forward_bf16_interleaved,
     gpu_flash_attention_forward_via_bf16,
     gpu_flash_attention_supported,
+    set_decode_early_start,
 )
 
 __version__ = "0.1"

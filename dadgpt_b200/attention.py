@@ -237,6 +237,14 @@ def decode_attention_bf16(out, q, k_new, v_new, cache: KVCacheBF16, scale):
         cache.workspace.numel(), _stream()))
 
 
+def set_decode_early_start(on: bool) -> None:
+    """Let :func:`decode_attention_bf16` calls of this thread fetch the lengths and their first
+    cache rows while the kernel ahead of them in the stream drains. Only valid when that kernel
+    does not write this call's cache, lengths or workspace (layers of a model with two or more
+    layers, each with its own :class:`KVCacheBF16`); see include/dadattn.h."""
+    _lib.check(_lib.load().dadattn_set_decode_early_start(1 if on else 0))
+
+
 def device_status() -> int:
     """Synchronise and return (then clear) the device-side status word; 0 = no condition."""
     return int(_lib.load().dadattn_device_status(_stream()))

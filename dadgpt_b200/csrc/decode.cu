@@ -115,14 +115,17 @@ decode_splitk_kernel(T* __restrict__ out, float* __restrict__ partial,
                      const T* __restrict__ q, const T* __restrict__ k_new,
                      const T* __restrict__ v_new, T* __restrict__ k_cache, T* __restrict__ v_cache,
                      int32_t* __restrict__ lengths, int fixed_len, int H, int max_len, int chunk,
-                     int reorder, float scale, int* __restrict__ status) {
+                     int reorder, int early, float scale, int* __restrict__ status) {
   constexpr int EPL = Elem<T>::kPerLane;  // elements per lane (one 16-byte load)
   constexpr int LPK = D / EPL;            // lanes per cache row
   constexpr int KPI = 32 / LPK;           // cache rows per warp instruction
   static_assert(LPK >= 1 && LPK <= 32 && (LPK & (LPK - 1)) == 0, "row must split over a warp");
 
-  // Everything this grid reads may have been written by the grid before it.
-  pdl_wait();
+  // Everything this grid reads may have been written by the grid before it — unless the caller
+  // has promised (dadattn_set_decode_early_start) that the grid before it does not write this
+  // call's caches, lengths and workspace: then the lengths, the ranking and each warp's first
+  // cache rows are fetched while that grid drains, and only the token vectors wait for it.
+  if (!early) pdl_wait();
   pdl_launch_dependents();
 
   const int split = blockIdx.y, splits = gridDim.y;
@@ -226,16 +229,31 @@ decode_splitk_kernel(T* __restrict__ out, float* __restrict__ partial,
     const size_t vec_off = static_cast<size_t>(bh) * D + part * EPL;
     const size_t cache_base = static_cast<size_t>(bh) * max_len * D + part * EPL;
 
+    uint4 kr[kDecodeBatch], vr[kDecodeBatch];
+    bool ok[kDecodeBatch];
+    int base = row_begin + warp * KPI * kDecodeBatch;
+    // early start: the warp's first batch, if it lies wholly among the rows already in the cache
+    // (the row being appended needs k_new / v_new, which must wait)
+    const bool prefetched = early && base + KPI * kDecodeBatch <= len;
+    if (prefetched) {
+#pragma unroll
+      for (int u = 0; u < kDecodeBatch; ++u) {
+        const int row = base + u * KPI + slot;
+        ok[u] = true;
+        kr[u] = ld_stream(k_cache + cache_base + static_cast<size_t>(row) * D);
+        vr[u] = ld_stream(v_cache + cache_base + static_cast<size_t>(row) * D);
+      }
+    }
+    if (early) pdl_wait();
+
     float qf[EPL];
     Elem<T>::unpack(qf, *reinterpret_cast<const uint4*>(q + vec_off));
     float m = -FLT_MAX, l = 0.f, acc[EPL];
 #pragma unroll
     for (int e = 0; e < EPL; ++e) acc[e] = 0.f;
 
-    for (int base = row_begin + warp * KPI * kDecodeBatch; base < row_end;
-         base += kDecodeWarps * KPI * kDecodeBatch) {
-      uint4 kr[kDecodeBatch], vr[kDecodeBatch];
-      bool ok[kDecodeBatch];
+    for (bool first = true; base < row_end; base += kDecodeWarps * KPI * kDecodeBatch, first = false) {
+      if (!(first && prefetched)) {
 #pragma unroll
       for (int u = 0; u < kDecodeBatch; ++u) {
         const int row = base + u * KPI + slot;
@@ -253,6 +271,7 @@ decode_splitk_kernel(T* __restrict__ out, float* __restrict__ partial,
             vr[u] = ld_stream(v_cache + cache_base + static_cast<size_t>(row) * D);
           }
         }
+      }
       }
       float s[kDecodeBatch];
       float m_new = m;
@@ -368,7 +387,7 @@ template <int DH>
 int launch_decode_bf16(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
                        const uint16_t* v_new, uint16_t* k_cache, uint16_t* v_cache,
                        int32_t* lengths, int B, int H, int max_len, float scale,
-                       unsigned* tickets, float* partial, int* status, cudaStream_t st) {
+                       unsigned* tickets, float* partial, int* status, int early, cudaStream_t st) {
   using T = __nv_bfloat16;
   const int chunk = chunk_rows(B, H, max_len);
   const int splits = split_count(B, H, max_len);
@@ -386,7 +405,7 @@ int launch_decode_bf16(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
                              reinterpret_cast<const T*>(q), reinterpret_cast<const T*>(k_new),
                              reinterpret_cast<const T*>(v_new), reinterpret_cast<T*>(k_cache),
                              reinterpret_cast<T*>(v_cache), lengths, 0, H, max_len, chunk, reorder,
-                             scale, status));
+                             early, scale, status));
   return DADATTN_OK;
 }
 
@@ -404,6 +423,8 @@ int check_decode_bf16(const void* out, const void* q, const void* k_new, const v
     return fail(DADATTN_E_ARG, "decode: pointers must be 16-byte aligned");
   return DADATTN_OK;
 }
+
+thread_local int g_decode_early = 0;
 
 }  // namespace
 }  // namespace dadattn
@@ -433,9 +454,14 @@ extern "C" int dadattn_decode_bf16(uint16_t* out, const uint16_t* q, const uint1
   unsigned* tickets = static_cast<unsigned*>(workspace);
   float* partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + ticket_bytes(B, H));
   return D == 64 ? launch_decode_bf16<64>(out, q, k_new, v_new, k_cache, v_cache, lengths, B, H,
-                                          max_len, scale, tickets, partial, status, st)
+                                          max_len, scale, tickets, partial, status, g_decode_early, st)
                  : launch_decode_bf16<128>(out, q, k_new, v_new, k_cache, v_cache, lengths, B, H,
-                                           max_len, scale, tickets, partial, status, st);
+                                           max_len, scale, tickets, partial, status, g_decode_early, st);
+}
+
+extern "C" int dadattn_set_decode_early_start(int on) {
+  g_decode_early = on ? 1 : 0;
+  return DADATTN_OK;
 }
 
 extern "C" int dadattn_decode_f32(float* out, const float* q, const float* k_new,
@@ -462,7 +488,7 @@ extern "C" int dadattn_decode_f32(float* out, const float* q, const float* k_new
                                static_cast<float*>(nullptr), static_cast<unsigned*>(nullptr),   \
                                static_cast<unsigned*>(nullptr), q, k_new, v_new, k_cache,       \
                                v_cache, static_cast<int32_t*>(nullptr), pos, H, max_len,        \
-                               max_len, 0, scale, status));                                     \
+                               max_len, 0, 0, scale, status));                                  \
     break;
   switch (D) {
     DAD_DECODE32(16) DAD_DECODE32(32) DAD_DECODE32(64) DAD_DECODE32(128)
@@ -549,10 +575,11 @@ extern "C" int dadattn_decode_bf16_noalloc(uint16_t* out, const uint16_t* q,
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   unsigned* tickets = reinterpret_cast<unsigned*>(scratch);
   float* partial = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + kNoAllocTicketBytes);
+  // never with early start: every call shares the one scratch array with the call before it
   return D == 64 ? launch_decode_bf16<64>(out, q, k_new, v_new, k_cache, v_cache, lengths, B, H,
-                                          max_len, scale, tickets, partial, status, st)
+                                          max_len, scale, tickets, partial, status, 0, st)
                  : launch_decode_bf16<128>(out, q, k_new, v_new, k_cache, v_cache, lengths, B, H,
-                                           max_len, scale, tickets, partial, status, st);
+                                           max_len, scale, tickets, partial, status, 0, st);
 }
 
 extern "C" int dadattn_decode_noalloc_status(dadattn_stream_t stream) {

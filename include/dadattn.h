@@ -250,6 +250,18 @@ int dadattn_decode_bf16(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
                         int32_t* lengths, int B, int H, int D, int max_len, float scale,
                         void* workspace, size_t workspace_bytes, dadattn_stream_t stream);
 
+/* Lets dadattn_decode_bf16 calls of the calling thread start early: the kernel reads `lengths`
+ * and each warp's first cache rows while the kernel ahead of it in the stream is still draining,
+ * and waits for that kernel only before it touches q, k_new and v_new. The caller thereby
+ * promises that the kernel ahead does not write THIS call's k_cache, v_cache, lengths or
+ * workspace. That holds for the layers of a model with two or more layers, each with its own
+ * cache and workspace (the call ahead of layer l's attention is layer l's projection, and the
+ * previous write to this cache was a whole step ago); it does not hold for back-to-back calls
+ * on one cache, which would see a stale length. 0 (the default) restores the fully ordered
+ * behaviour. dadattn_decode_bf16_noalloc and dadattn_decode_f32 never start early. No counterpart
+ * in the reference. */
+int dadattn_set_decode_early_start(int on);
+
 /* dadattn_decode_bf16 for callers that cannot allocate device memory or hand over a workspace
  * (no counterpart in the reference). Typical cases: a server that gave all remaining HBM to its
  * own KV-cache pool at start-up, a decode loop that must not hit the device-wide stall of an

@@ -123,6 +123,41 @@ def test_full_sequence_is_skipped_and_reported(cuda):
     assert (out[1] == 0).all() and device_status() == 0
 
 
+def test_early_start_over_rotating_layer_caches(cuda, oracle):
+    """dadattn_set_decode_early_start with the use it is meant for: several layer caches, each
+    with its own lengths and workspace, decoded one after the other for several steps, so that
+    the kernel ahead of a call always belongs to another cache. Every layer's output, appended
+    rows and lengths are checked against the oracle at every step."""
+    layers, B, H, L, D, scale = 3, 40, 12, 300, 64, 0.125
+    g = torch.Generator(device=cuda).manual_seed(5)
+    caches = [dad.KVCacheBF16(B, H, L, D, device=cuda) for _ in range(layers)]
+    lens0 = torch.randint(1, 250, (B,), generator=torch.Generator().manual_seed(6), dtype=torch.int32)
+    for c in caches:
+        c.k.copy_(torch.randn(c.k.shape, device=cuda, generator=g))
+        c.v.copy_(torch.randn(c.v.shape, device=cuda, generator=g))
+        c.lengths.copy_(lens0.to(cuda))
+    dad.set_decode_early_start(True)
+    try:
+        for step in range(3):
+            q, kn, vn = (torch.randn(layers, B, H, D, device=cuda, generator=g).to(torch.bfloat16) for _ in range(3))
+            out = torch.full_like(q, float("nan"))
+            for l, c in enumerate(caches):   # back to back, no synchronisation in between
+                dad.decode_attention_bf16(out[l], q[l], kn[l], vn[l], c, scale)
+            torch.cuda.synchronize()
+            now = (lens0 + step + 1).numpy().astype(np.int32)
+            for l, c in enumerate(caches):
+                assert (c.lengths.cpu().numpy() == now).all()
+                want = oracle.decode(q[l].float().cpu().numpy(), c.k.float().cpu().numpy(),
+                                     c.v.float().cpu().numpy(), now, scale)
+                assert max_abs(out[l].float().cpu().numpy(), want) <= 2e-2
+                rows = torch.from_numpy(now.astype(np.int64) - 1).to(cuda)
+                ar = torch.arange(B, device=cuda)
+                assert torch.equal(c.k[ar, :, rows], kn[l]) and torch.equal(c.v[ar, :, rows], vn[l])
+    finally:
+        dad.set_decode_early_start(False)
+    assert device_status() == 0
+
+
 @pytest.mark.parametrize("graph", [False, True], ids=["plain", "graph"])
 def test_decode_at_the_benchmark_configuration(cuda, oracle, graph):
     """The exact decode configuration bench.py times: 64 sequences, 12 heads, head size 64,
