@@ -230,7 +230,6 @@ decode_splitk_kernel(T* __restrict__ out, float* __restrict__ partial,
     const size_t cache_base = static_cast<size_t>(bh) * max_len * D + part * EPL;
 
     uint4 kr[kDecodeBatch], vr[kDecodeBatch];
-    bool ok[kDecodeBatch];
     int base = row_begin + warp * KPI * kDecodeBatch;
     // early start: the warp's first batch, if it lies wholly among the rows already in the cache
     // (the row being appended needs k_new / v_new, which must wait)
@@ -239,7 +238,6 @@ decode_splitk_kernel(T* __restrict__ out, float* __restrict__ partial,
 #pragma unroll
       for (int u = 0; u < kDecodeBatch; ++u) {
         const int row = base + u * KPI + slot;
-        ok[u] = true;
         kr[u] = ld_stream(k_cache + cache_base + static_cast<size_t>(row) * D);
         vr[u] = ld_stream(v_cache + cache_base + static_cast<size_t>(row) * D);
       }
@@ -252,15 +250,15 @@ decode_splitk_kernel(T* __restrict__ out, float* __restrict__ partial,
 #pragma unroll
     for (int e = 0; e < EPL; ++e) acc[e] = 0.f;
 
-    for (bool first = true; base < row_end; base += kDecodeWarps * KPI * kDecodeBatch, first = false) {
-      if (!(first && prefetched)) {
+    bool fetched = prefetched;   // the batch at `base` is already in registers
+    for (; base < row_end; base += kDecodeWarps * KPI * kDecodeBatch, fetched = false) {
+      if (!fetched) {
 #pragma unroll
       for (int u = 0; u < kDecodeBatch; ++u) {
         const int row = base + u * KPI + slot;
-        ok[u] = row < row_end;
         kr[u] = make_uint4(0, 0, 0, 0);
         vr[u] = make_uint4(0, 0, 0, 0);
-        if (ok[u]) {
+        if (row < row_end) {
           if (row == len) {  // the token being appended: use its vectors and store them
             kr[u] = *reinterpret_cast<const uint4*>(k_new + vec_off);
             vr[u] = *reinterpret_cast<const uint4*>(v_new + vec_off);
@@ -284,7 +282,7 @@ decode_splitk_kernel(T* __restrict__ out, float* __restrict__ partial,
         for (int e = 0; e < EPL; ++e) dot = fmaf(qf[e], kf[e], dot);
 #pragma unroll
         for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        s[u] = ok[u] ? dot * scale : -FLT_MAX;
+        s[u] = (base + u * KPI + slot < row_end) ? dot * scale : -FLT_MAX;
         m_new = fmaxf(m_new, s[u]);
       }
       if (m_new > -FLT_MAX) {  // at least one row seen by this lane group so far
@@ -294,7 +292,7 @@ decode_splitk_kernel(T* __restrict__ out, float* __restrict__ partial,
         for (int e = 0; e < EPL; ++e) acc[e] *= corr;
 #pragma unroll
         for (int u = 0; u < kDecodeBatch; ++u) {
-          if (!ok[u]) continue;
+          if (!(base + u * KPI + slot < row_end)) continue;
           const float p = expf(s[u] - m_new);
           l += p;
           float vf[EPL];
