@@ -529,44 +529,42 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tc_fence_before_sync();
             mbar_arrive(&bars->x_free);  // scores are in registers: the next tile's GEMMs may overwrite
           }
-          // ds = p (dP - delta) scale as p * fma(dP, scale, -delta scale); the causal compare
-          // only exists on an item's first (diagonal) tile
-          auto elem = [&](int cc, bool masked, float& pd, float& ds) {
+          // ds = p (dP - delta) scale as p * fma(dP, scale, -delta scale), two columns at a time
+          // with packed two-float instructions; the causal compare only exists on an item's first
+          // (diagonal) tile
+          auto pair = [&](int cc, bool masked, uint32_t& pw_, uint32_t& dw_) {
             const int key = k0 + cg * 32 + h * 16 + cc;
-            float p = ex2(fmaf(__uint_as_float(x1[cc]), scale_log2, -row_lse2));
-            if (masked && key > q) p = 0.f;
-            float gr = __uint_as_float(x2[cc]);
-            pd = p;
+            const float2 e = ffma2(make_float2(__uint_as_float(x1[cc]), __uint_as_float(x1[cc + 1])),
+                                   make_float2(scale_log2, scale_log2), make_float2(-row_lse2, -row_lse2));
+            float2 p = make_float2(ex2(e.x), ex2(e.y));
+            if (masked) {
+              if (key > q) p.x = 0.f;
+              if (key + 1 > q) p.y = 0.f;
+            }
+            float2 gr = make_float2(__uint_as_float(x2[cc]), __uint_as_float(x2[cc + 1]));
+            float2 pd = p;
             if (DROP == 1) {
               const uint64_t idx = (static_cast<uint64_t>(unit0 + t.bh) * S + q) * S + key;
-              const float mk = (p != 0.f && philox_keep(rng, idx, rate)) ? keep_scale : 0.f;
-              pd = p * mk;
-              gr *= mk;
+              const float m0 = (p.x != 0.f && philox_keep(rng, idx, rate)) ? keep_scale : 0.f;
+              const float m1 = (p.y != 0.f && philox_keep(rng, idx + 1, rate)) ? keep_scale : 0.f;
+              pd = fmul2(p, make_float2(m0, m1));
+              gr = fmul2(gr, make_float2(m0, m1));
             } else if (DROP == 2) {
-              const float mk = ((keep_word >> (h * 16 + cc)) & 1u) ? keep_scale : 0.f;
-              pd = p * mk;
-              gr *= mk;
+              const float m0 = ((keep_word >> (h * 16 + cc)) & 1u) ? keep_scale : 0.f;
+              const float m1 = ((keep_word >> (h * 16 + cc + 1)) & 1u) ? keep_scale : 0.f;
+              pd = fmul2(p, make_float2(m0, m1));
+              gr = fmul2(gr, make_float2(m0, m1));
             }
-            ds = p * fmaf(gr, scale, -row_delta_s);
+            const float2 ds = fmul2(p, ffma2(gr, make_float2(scale, scale), make_float2(-row_delta_s, -row_delta_s)));
+            pw_ = pack_bf16(pd.x, pd.y);
+            dw_ = pack_bf16(ds.x, ds.y);
           };
           if (diagonal) {
 #pragma unroll
-            for (int cc = 0; cc < 16; cc += 2) {
-              float p0, p1, d0, d1;
-              elem(cc, true, p0, d0);
-              elem(cc + 1, true, p1, d1);
-              pw[h * 8 + cc / 2] = pack_bf16(p0, p1);
-              dw[h * 8 + cc / 2] = pack_bf16(d0, d1);
-            }
+            for (int cc = 0; cc < 16; cc += 2) pair(cc, true, pw[h * 8 + cc / 2], dw[h * 8 + cc / 2]);
           } else {
 #pragma unroll
-            for (int cc = 0; cc < 16; cc += 2) {
-              float p0, p1, d0, d1;
-              elem(cc, false, p0, d0);
-              elem(cc + 1, false, p1, d1);
-              pw[h * 8 + cc / 2] = pack_bf16(p0, p1);
-              dw[h * 8 + cc / 2] = pack_bf16(d0, d1);
-            }
+            for (int cc = 0; cc < 16; cc += 2) pair(cc, false, pw[h * 8 + cc / 2], dw[h * 8 + cc / 2]);
           }
         }
         // P / dS of tile g-1 consumed and its dQ complete in tensor memory
