@@ -41,6 +41,8 @@ SIGNATURES = {
     "dadattn_decode_f32": (I, [P] * 6 + [I, I, I, I, F, P]),
     "dadattn_decode_workspace_bytes": (SZ, [I, I, I, I]),
     "dadattn_decode_bf16": (I, [P] * 7 + [I, I, I, I, F, P, SZ, P]),
+    "dadattn_decode_f32_batched": (I, [P] * 7 + [I, I, I, I, F, P, SZ, P]),
+    "dadattn_kv_cache_fill": (I, [P, P, P, P, P, I, I, I, I, I, I, I, P]),
     "dadattn_set_decode_early_start": (I, [I]),
     "dadattn_decode_bf16_noalloc": (I, [P] * 7 + [I, I, I, I, F, P]),
     "dadattn_decode_noalloc_status": (I, [P]),

@@ -381,12 +381,10 @@ decode_splitk_kernel(T* __restrict__ out, float* __restrict__ partial,
   advance_lengths();
 }
 
-template <int DH>
-int launch_decode_bf16(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
-                       const uint16_t* v_new, uint16_t* k_cache, uint16_t* v_cache,
-                       int32_t* lengths, int B, int H, int max_len, float scale,
-                       unsigned* tickets, float* partial, int* status, int early, cudaStream_t st) {
-  using T = __nv_bfloat16;
+template <typename T, typename Raw, int DH>
+int launch_decode_batched(Raw* out, const Raw* q, const Raw* k_new, const Raw* v_new, Raw* k_cache,
+                          Raw* v_cache, int32_t* lengths, int B, int H, int max_len, float scale,
+                          unsigned* tickets, float* partial, int* status, int early, cudaStream_t st) {
   const int chunk = chunk_rows(B, H, max_len);
   const int splits = split_count(B, H, max_len);
   unsigned* seq_tickets = tickets + static_cast<size_t>(B) * H;
@@ -405,6 +403,40 @@ int launch_decode_bf16(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
                              reinterpret_cast<T*>(v_cache), lengths, 0, H, max_len, chunk, reorder,
                              early, scale, status));
   return DADATTN_OK;
+}
+
+template <int DH>
+int launch_decode_bf16(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
+                       const uint16_t* v_new, uint16_t* k_cache, uint16_t* v_cache,
+                       int32_t* lengths, int B, int H, int max_len, float scale,
+                       unsigned* tickets, float* partial, int* status, int early, cudaStream_t st) {
+  return launch_decode_batched<__nv_bfloat16, uint16_t, DH>(out, q, k_new, v_new, k_cache, v_cache, lengths, B,
+                                                            H, max_len, scale, tickets, partial, status,
+                                                            early, st);
+}
+
+// Rows 0..n-1 of sequence b's cache from the K / V heads a prefill leaves behind: k_heads,
+// v_heads [H, n, D] fp32 (the reference's q_heads / k_heads / v_heads layout for batch 1,
+// src/model.cpp:385-387) -> k_cache, v_cache [B, H, max_len, D] in T; sets lengths[b] = n. One
+// launch for both tensors; the reference does two cudaMemcpy2D per layer (src/model.cpp:835-843).
+template <typename T>
+__global__ void kv_cache_fill_kernel(T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                     int32_t* __restrict__ lengths, const float* __restrict__ k_heads,
+                                     const float* __restrict__ v_heads, int b, int H, int n, int max_len,
+                                     int D) {
+  const int64_t per = static_cast<int64_t>(H) * n * D / 4;   // float4 groups per tensor
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t == 0 && lengths) lengths[b] = n;
+  if (t >= 2 * per) return;
+  const bool is_v = t >= per;
+  const int64_t i = (is_v ? t - per : t) * 4;         // element index in [H, n, D]
+  const int64_t h = i / (static_cast<int64_t>(n) * D), rem = i - h * n * D;
+  const float4 x = *reinterpret_cast<const float4*>((is_v ? v_heads : k_heads) + i);
+  T* dst = (is_v ? v_cache : k_cache) + ((static_cast<int64_t>(b) * H + h) * max_len) * D + rem;
+  dst[0] = Elem<T>::from_float(x.x);
+  dst[1] = Elem<T>::from_float(x.y);
+  dst[2] = Elem<T>::from_float(x.z);
+  dst[3] = Elem<T>::from_float(x.w);
 }
 
 int check_decode_bf16(const void* out, const void* q, const void* k_new, const void* v_new,
@@ -594,4 +626,58 @@ extern "C" int dadattn_decode_noalloc_status(dadattn_stream_t stream) {
   else if (host != 0)
     fail(host, "decode (no-alloc): device status %d", host);
   return host;
+}
+
+// Batched decode on fp32 caches: the arithmetic of dadattn_decode_f32 for many sequences at once.
+extern "C" int dadattn_decode_f32_batched(float* out, const float* q, const float* k_new, const float* v_new,
+                                          float* k_cache, float* v_cache, int32_t* lengths, int B, int H,
+                                          int D, int max_len, float scale, void* workspace,
+                                          size_t workspace_bytes_given, dadattn_stream_t stream) {
+  if (!out || !q || !k_new || !v_new || !k_cache || !v_cache || !lengths)
+    return fail(DADATTN_E_ARG, "decode: null pointer");
+  if (B <= 0 || H <= 0 || max_len <= 0 || H > 65535 || static_cast<long long>(B) * H > 0x7fffffffLL)
+    return fail(DADATTN_E_ARG, "decode: bad sizes B=%d H=%d max_len=%d", B, H, max_len);
+  if (D != 16 && D != 32 && D != 64 && D != 128)
+    return fail(DADATTN_E_UNSUPPORTED, "decode f32: unsupported D %d", D);
+  if (!aligned(out, 16) || !aligned(q, 16) || !aligned(k_new, 16) || !aligned(v_new, 16) ||
+      !aligned(k_cache, 16) || !aligned(v_cache, 16))
+    return fail(DADATTN_E_ARG, "decode: pointers must be 16-byte aligned");
+  if (!workspace || !aligned(workspace, 16))
+    return fail(DADATTN_E_ARG, "decode: workspace must be a 16-byte aligned device pointer");
+  if (workspace_bytes_given < workspace_bytes(B, H, D, max_len))
+    return fail(DADATTN_E_WORKSPACE, "decode: workspace %zu < %zu bytes", workspace_bytes_given,
+                workspace_bytes(B, H, D, max_len));
+  int* status = device_status_word();
+  if (!status) return DADATTN_E_CUDA;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  unsigned* tickets = static_cast<unsigned*>(workspace);
+  float* partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + ticket_bytes(B, H));
+  switch (D) {
+    case 16: return launch_decode_batched<float, float, 16>(out, q, k_new, v_new, k_cache, v_cache, lengths, B, H, max_len, scale, tickets, partial, status, 0, st);
+    case 32: return launch_decode_batched<float, float, 32>(out, q, k_new, v_new, k_cache, v_cache, lengths, B, H, max_len, scale, tickets, partial, status, 0, st);
+    case 64: return launch_decode_batched<float, float, 64>(out, q, k_new, v_new, k_cache, v_cache, lengths, B, H, max_len, scale, tickets, partial, status, 0, st);
+    default: return launch_decode_batched<float, float, 128>(out, q, k_new, v_new, k_cache, v_cache, lengths, B, H, max_len, scale, tickets, partial, status, 0, st);
+  }
+}
+
+extern "C" int dadattn_kv_cache_fill(void* k_cache, void* v_cache, int32_t* lengths, const float* k_heads,
+                                     const float* v_heads, int b, int B, int H, int n, int max_len, int D,
+                                     int cache_is_bf16, dadattn_stream_t stream) {
+  if (!k_cache || !v_cache || !k_heads || !v_heads) return fail(DADATTN_E_ARG, "cache fill: null pointer");
+  if (B <= 0 || H <= 0 || D <= 0 || D % 4 != 0 || b < 0 || b >= B || n < 1 || n > max_len)
+    return fail(DADATTN_E_ARG, "cache fill: bad sizes b=%d B=%d H=%d n=%d max_len=%d D=%d", b, B, H, n, max_len, D);
+  if (!aligned(k_heads, 16) || !aligned(v_heads, 16))
+    return fail(DADATTN_E_ARG, "cache fill: k_heads / v_heads must be 16-byte aligned");
+  const int64_t groups = 2 * (static_cast<int64_t>(H) * n * D / 4);
+  const unsigned blocks = static_cast<unsigned>((groups + 255) / 256);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cache_is_bf16)
+    kv_cache_fill_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(static_cast<__nv_bfloat16*>(k_cache),
+                                                                static_cast<__nv_bfloat16*>(v_cache), lengths,
+                                                                k_heads, v_heads, b, H, n, max_len, D);
+  else
+    kv_cache_fill_kernel<float><<<blocks, 256, 0, st>>>(static_cast<float*>(k_cache), static_cast<float*>(v_cache),
+                                                        lengths, k_heads, v_heads, b, H, n, max_len, D);
+  DAD_LAUNCH_CHECK("kv_cache_fill_kernel");
+  return DADATTN_OK;
 }

@@ -96,3 +96,21 @@ void gpu_decode_attention(float* out, const float* q, const float* k_new, const 
                          nullptr) != DADATTN_OK)
     throw std::runtime_error(std::string("CUDA error: ") + dadattn_last_error());
 }
+
+void gpu_decode_attention_batched(float* out, const float* q, const float* k_new, const float* v_new,
+                                  float* k_cache, float* v_cache, int* lengths, int batch, int n_heads,
+                                  int max_len, int d_head, float scale, void* workspace,
+                                  size_t workspace_bytes) {
+  if (dadattn_decode_f32_batched(out, q, k_new, v_new, k_cache, v_cache, lengths, batch, n_heads, d_head,
+                                 max_len, scale, workspace, workspace_bytes, nullptr) != DADATTN_OK)
+    throw std::runtime_error(std::string("CUDA error: ") + dadattn_last_error());
+}
+
+void gpu_kv_cache_fill(float* k_cache, float* v_cache, int* lengths, const float* k_heads,
+                       const float* v_heads, int b, int batch, int n_heads, int n, int max_len,
+                       int d_head) {
+  if (n < 1 || n > max_len) throw std::out_of_range("gpu_kv_cache_fill: bad prompt length");
+  if (dadattn_kv_cache_fill(k_cache, v_cache, lengths, k_heads, v_heads, b, batch, n_heads, n, max_len,
+                            d_head, 0, nullptr) != DADATTN_OK)
+    throw std::runtime_error(std::string("CUDA error: ") + dadattn_last_error());
+}

@@ -250,6 +250,26 @@ int dadattn_decode_bf16(uint16_t* out, const uint16_t* q, const uint16_t* k_new,
                         int32_t* lengths, int B, int H, int D, int max_len, float scale,
                         void* workspace, size_t workspace_bytes, dadattn_stream_t stream);
 
+/* dadattn_decode_f32 for B sequences at once, on fp32 caches [B,H,max_len,D] with lengths[B] as in
+ * dadattn_decode_bf16 (same workspace rules, dadattn_decode_workspace_bytes). Head sizes 16, 32,
+ * 64, 128. This is what a batched generation loop over the reference's fp32 model calls once per
+ * layer; results equal B separate dadattn_decode_f32 calls. No counterpart in the reference, which
+ * decodes one sequence at a time (src/generate.cpp:94-139). */
+int dadattn_decode_f32_batched(float* out, const float* q, const float* k_new, const float* v_new,
+                               float* k_cache, float* v_cache, int32_t* lengths, int B, int H, int D,
+                               int max_len, float scale, void* workspace, size_t workspace_bytes,
+                               dadattn_stream_t stream);
+
+/* Fills sequence b of a batched cache from a prefill: k_heads, v_heads [H, n, D] fp32 (what the
+ * reference's model_forward leaves in k_heads / v_heads for batch 1) go to rows 0..n-1 of
+ * k_cache, v_cache [B,H,max_len,D] — bf16 (rounded to nearest even) when cache_is_bf16, else fp32
+ * — and lengths[b] becomes n (lengths may be NULL). One launch for both tensors; replaces the two
+ * cudaMemcpy2D per layer of model_prefill (reference src/model.cpp:835-843), which can neither
+ * convert nor address a batch entry. */
+int dadattn_kv_cache_fill(void* k_cache, void* v_cache, int32_t* lengths, const float* k_heads,
+                          const float* v_heads, int b, int B, int H, int n, int max_len, int D,
+                          int cache_is_bf16, dadattn_stream_t stream);
+
 /* Lets dadattn_decode_bf16 calls of the calling thread start early: the kernel reads `lengths`
  * and each warp's first cache rows while the kernel ahead of it in the stream is still draining,
  * and waits for that kernel only before it touches q, k_new and v_new. The caller thereby

@@ -7,6 +7,8 @@
  */
 #pragma once
 
+#include <cstddef>
+
 /* Fused causal attention WITH attention-probability dropout: what the reference computes in its
  * materialized branch (src/model.cpp:406-415 forward, :595-602 backward) when
  * use_fused_attention (src/model.cpp:185-197) has to decline because dropout is on. `seed` is
@@ -34,3 +36,19 @@ void gpu_flash_attention_backward_dropout(float* dq, float* dk, float* dv, float
 void gpu_decode_attention(float* out, const float* q, const float* k_new, const float* v_new,
                           float* k_cache, float* v_cache, int n_heads, int max_len, int d_head,
                           int pos, float scale);
+
+/* The same for `batch` sequences at once: caches [batch, n_heads, max_len, d_head] fp32, device
+ * array lengths[batch] (each sequence's current length; advanced by one), q / k_new / v_new / out
+ * [batch, n_heads * d_head]. `workspace` as dadattn_decode_workspace_bytes says, zero-filled once.
+ * For a generation loop that decodes several sequences per step. */
+void gpu_decode_attention_batched(float* out, const float* q, const float* k_new, const float* v_new,
+                                  float* k_cache, float* v_cache, int* lengths, int batch, int n_heads,
+                                  int max_len, int d_head, float scale, void* workspace,
+                                  size_t workspace_bytes);
+
+/* Rows 0..n-1 of sequence b of a batched fp32 cache from the k_heads / v_heads [n_heads, n, d_head]
+ * a batch-1 model_forward leaves behind (what model_prefill copies with cudaMemcpy2D,
+ * src/model.cpp:835-843); lengths[b] = n. */
+void gpu_kv_cache_fill(float* k_cache, float* v_cache, int* lengths, const float* k_heads,
+                       const float* v_heads, int b, int batch, int n_heads, int n, int max_len,
+                       int d_head);

@@ -84,7 +84,7 @@ def test_gpuops_shim_defines_the_reference_symbols():
                 assert name in ref
     # additions declared in include/dadattn_gpu_ops.hpp
     for sym in ("gpu_flash_attention_forward_dropout", "gpu_flash_attention_backward_dropout",
-                "gpu_decode_attention"):
+                "gpu_decode_attention", "gpu_decode_attention_batched", "gpu_kv_cache_fill"):
         assert sym in out, sym
 
 

@@ -212,3 +212,57 @@ def test_decode_at_the_benchmark_configuration(cuda, oracle, graph):
         want = oracle.decode(q.float().cpu().numpy(), kc, vc, now.astype(np.int32), cfg.scale)
         assert max_abs(out.float().cpu().numpy(), want) <= 2e-2
     assert device_status() == 0
+
+
+@pytest.mark.parametrize("D", [32, 64])
+def test_batched_f32_decode_and_cache_fill(cuda, oracle, D):
+    """dadattn_kv_cache_fill (a prefill's [H, n, D] heads into rows 0..n-1 of one sequence of a
+    batched cache, fp32 and bf16) and dadattn_decode_f32_batched against the oracle and against
+    one dadattn_decode_f32 call per sequence."""
+    from dadgpt_b200 import _lib
+    lib = _lib.load()
+    B, H, L, scale = 5, 4, 96, D ** -0.5
+    stream = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator(device=cuda).manual_seed(D)
+    kc = torch.zeros(B, H, L, D, device=cuda)
+    vc = torch.zeros_like(kc)
+    kb, vb = kc.to(torch.bfloat16), vc.to(torch.bfloat16)
+    lens = torch.zeros(B, dtype=torch.int32, device=cuda)
+    prompts = [1, 17, 40, 63, 95]
+    heads = []
+    for b, n in enumerate(prompts):
+        kh, vh = (torch.randn(H, n, D, device=cuda, generator=g) for _ in range(2))
+        heads.append((kh, vh))
+        for cache_k, cache_v, is_bf16, ln in ((kc, vc, 0, lens), (kb, vb, 1, None)):
+            rc = lib.dadattn_kv_cache_fill(cache_k.data_ptr(), cache_v.data_ptr(),
+                                           ln.data_ptr() if ln is not None else None, kh.data_ptr(),
+                                           vh.data_ptr(), b, B, H, n, L, D, is_bf16, stream)
+            assert rc == 0, lib.dadattn_last_error()
+    torch.cuda.synchronize()
+    assert lens.tolist() == prompts
+    for b, (kh, vh) in enumerate(heads):
+        n = prompts[b]
+        assert torch.equal(kc[b, :, :n], kh) and torch.equal(vc[b, :, :n], vh)
+        assert (kc[b, :, n:] == 0).all()
+        assert torch.equal(kb[b, :, :n], kh.to(torch.bfloat16)) and torch.equal(vb[b, :, :n], vh.to(torch.bfloat16))
+    # one batched decode step against the oracle and against per-sequence calls
+    ws_bytes = lib.dadattn_decode_workspace_bytes(B, H, D, L)
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=cuda)
+    q, kn, vn = (torch.randn(B, H, D, device=cuda, generator=g) for _ in range(3))
+    out = torch.full_like(q, float("nan"))
+    single_k, single_v = kc.clone(), vc.clone()
+    rc = lib.dadattn_decode_f32_batched(out.data_ptr(), q.data_ptr(), kn.data_ptr(), vn.data_ptr(), kc.data_ptr(),
+                                        vc.data_ptr(), lens.data_ptr(), B, H, D, L, scale, ws.data_ptr(),
+                                        ws_bytes, stream)
+    assert rc == 0, lib.dadattn_last_error()
+    torch.cuda.synchronize()
+    assert lens.tolist() == [n + 1 for n in prompts]
+    want = oracle.decode(q.cpu().numpy(), kc.cpu().numpy(), vc.cpu().numpy(), lens.cpu().numpy(), scale)
+    assert max_abs(out.cpu().numpy(), want) <= 1e-5
+    for b, n in enumerate(prompts):
+        o1 = torch.empty(H, D, device=cuda)
+        dad.decode_attention_f32(o1, q[b].contiguous(), kn[b].contiguous(), vn[b].contiguous(), single_k[b],
+                                 single_v[b], n, scale)
+        assert (o1 - out[b]).abs().max().item() <= 1e-5
+        assert torch.equal(single_k[b], kc[b]) and torch.equal(single_v[b], vc[b])
+    assert device_status() == 0

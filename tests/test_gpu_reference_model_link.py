@@ -50,3 +50,5 @@ def test_patched_reference_model_reaches_fused_dropout_and_one_launch_decode(cud
     assert sum(l.startswith("fused_dropout_vs_materialized") and l.endswith(" OK") for l in lines) == 2
     assert sum(l.startswith("prefill_then_one_launch_decode") and l.endswith(" OK") for l in lines) == 2
     assert any(l.startswith("cached_decode") and "ms/token" in l for l in lines)
+    assert any(l.startswith("batched_generation 4 sequences") and l.endswith(" OK") for l in lines)
+    assert any(l.startswith("batched_generation gpt2-124m") and "ms/token" in l for l in lines)
