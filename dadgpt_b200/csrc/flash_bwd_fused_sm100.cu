@@ -455,16 +455,30 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // share a row need the same two values; only the first of them (column group 0: 128 threads)
     // loads them, one tile ahead, and hands them over through one of two shared-memory buffers:
     // global loads of the compute warps queue behind the dQ reduce traffic on the SM's path to
-    // L2, so there should be few of them and none whose latency is exposed. Queries beyond S
-    // contribute nothing (p = exp2(-inf) = 0).
+    // L2, so there should be few of them and none whose latency is exposed. The loaded words are
+    // therefore not touched before the tile after: an instruction that uses one (a scale, a
+    // select) would hold its warp, and through the tile's barriers all sixteen, until the load
+    // is back. Out-of-range rows load a valid address and are replaced when the values are
+    // published. Queries beyond S contribute nothing (p = exp2(-inf) = 0).
     float* vec = reinterpret_cast<float*>(smem + L::kVec);
-    auto load_row = [&](bool valid, int q_tile, int bh, float& l2, float& dl) {
-      if (cg != 0) return;
+    struct RowLoad { float lse, delta; bool in; };
+    auto load_row = [&](bool valid, int q_tile, int bh) -> RowLoad {
+      RowLoad r{0.f, 0.f, false};
+      if (cg != 0) return r;
       const int qq = q_tile * kFT + row;
-      const bool in = valid && qq < S;
-      const size_t at = static_cast<size_t>(bh) * S + qq;
-      l2 = in ? lse[at] * kFLog2e : INFINITY;
-      dl = in ? delta[at] : 0.f;
+      r.in = valid && qq < S;
+      const size_t at = r.in ? static_cast<size_t>(bh) * S + qq : 0;
+      r.lse = lse[at];
+      r.delta = delta[at];
+      return r;
+    };
+    // column group 0 publishes the scalars of tile g (buffer g % 2)
+    auto publish_row = [&](const RowLoad& r, int g) {
+      if (cg != 0) return;
+      float* vb = vec + (g & 1) * 256;
+      vb[row] = r.in ? r.lse * kFLog2e : INFINITY;
+      vb[128 + row] = r.in ? r.delta * scale : 0.f;
+      mbar_arrive(&bars->vec_full[g & 1]);
     };
 
     // Keep bits of this thread's 32 key columns for one tile: word cg of the row's record,
@@ -477,11 +491,11 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     ItemFeed feed{bars, abort_flag, 0};
     int cur = feed.fetch(n_items);
     int nxt = cur < n_items ? feed.fetch(n_items) : n_items;
-    float next_lse2 = INFINITY, next_delta = 0.f;
+    RowLoad next_row{0.f, 0.f, false};
     uint32_t keep_word = 0u, next_keep = 0u;
     if (cur < n_items) {
       const Item t0 = decode_item(cur, BH, n_tiles, group_bh);
-      load_row(true, t0.kt, t0.bh, next_lse2, next_delta);
+      publish_row(load_row(true, t0.kt, t0.bh), 0);
       if (DROP == 2) next_keep = load_keep(true, t0.kt, t0.kt, t0.bh);
     }
     int g = 0, j = 0;
@@ -493,25 +507,22 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int q = (t.kt + i) * kFT + row;
         const bool diagonal = (i == 0);
         const bool new_item = (i == 0 && j > 0);  // the item before this one is complete
-        // Buffer g % 2 was last read in tile g-2, which every thread had finished before the
-        // accumulating GEMMs of tile g-2 could complete, and this thread has seen them complete.
-        float* vbuf = vec + (g & 1) * 256;
-        if (cg == 0) {
-          vbuf[row] = next_lse2;
-          vbuf[128 + row] = next_delta * scale;
-          mbar_arrive(&bars->vec_full[g & 1]);
-        }
+        const float* vbuf = vec + (g & 1) * 256;
         if (DROP == 2) keep_word = next_keep;
+        // the next tile's scalars and keep bits: requested here, first touched after this tile's
+        // arithmetic
+        const bool more = (i + 1 < t.n_it) || nxt < n_items;
         if (i + 1 < t.n_it) {
-          load_row(true, t.kt + i + 1, t.bh, next_lse2, next_delta);
+          next_row = load_row(true, t.kt + i + 1, t.bh);
           if (DROP == 2) next_keep = load_keep(true, t.kt + i + 1, t.kt, t.bh);
         } else {
           const Item tn = decode_item(nxt < n_items ? nxt : 0, BH, n_tiles, group_bh);
-          load_row(nxt < n_items, tn.kt, tn.bh, next_lse2, next_delta);
+          next_row = load_row(nxt < n_items, tn.kt, tn.bh);
           if (DROP == 2) next_keep = load_keep(nxt < n_items, tn.kt, tn.kt, tn.bh);
         }
-        // (one barrier per buffer: the next completion of this one needs the GEMMs of tile g,
-        // hence this thread's own P / dS, so its phase cannot run away from a slow waiter)
+        // (one barrier per buffer: its next completion, for tile g+2, comes after the GEMMs of
+        // tile g have been seen complete, which need this thread's own P / dS of tile g, so the
+        // phase cannot run away from a slow waiter)
         if (!(ok = mbar_wait(&bars->vec_full[g & 1], (g >> 1) & 1, abort_flag))) break;
         const float row_lse2 = vbuf[row], row_delta_s = vbuf[128 + row];
         if (!(ok = mbar_wait(&bars->x_full, g & 1, abort_flag))) break;
@@ -572,6 +583,9 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (!(ok = mbar_wait(&bars->acc_done, (g - 1) & 1, abort_flag))) break;
           tc_fence_after_sync();
         }
+        // Scalars of tile g+1 into the other buffer: it was last read in tile g-1, which every
+        // thread had finished before the GEMMs seen complete just above could start.
+        if (more) publish_row(next_row, g + 1);
         // Across an item boundary tile g-1 also completed dK / dV of the previous item: take them
         // out of tensor memory before w_full lets this item's first GEMMs overwrite them.
         if (new_item) stage_dkv((j - 1) & 1);

@@ -54,14 +54,35 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 constexpr uint32_t kSpinLimit = 1u << 24;  // with the back-off below: a few seconds
+// Non-blocking polls before the suspending wait takes over. More than a few hundred cost time:
+// the polling of waiting warps competes for issue slots with the warps that still work.
+constexpr uint32_t kHotPolls = 128;
 
 // Waits for the phase with the given parity to complete. `abort_flag` (shared memory) is
 // polled too: once any thread of the CTA has given up, everybody leaves quickly. The thread
 // whose own wait runs out leaves `site` (the source line of the wait, through DAD_MBAR_WAIT)
 // in the flag, from where the kernel's exit path copies it next to the device status word.
+template <uint32_t HOT = kHotPolls>
 __device__ __forceinline__ bool mbar_wait_at(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                              int site) {
+  // Most waits in these kernels are short (a few hundred clocks: the next link of a pipeline). A
+  // suspending try_wait that has to be woken costs more than that, so the wait starts as a plain
+  // poll and only then turns into the suspending form with back-off.
+  for (uint32_t i = 0; i < HOT; ++i)
+    if (mbar_test_wait(bar, parity)) return true;
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 32) {

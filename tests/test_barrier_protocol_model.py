@@ -110,14 +110,18 @@ class Sim:
 
         g = 0
         j = 0
+        total = sum(self.items)
+        if total:
+            yield ("arrive", "vec_full[0]")               # the first tile's row scalars
         for j, n_it in enumerate(self.items):
             for i in range(n_it):
-                yield ("arrive", f"vec_full[{g & 1}]")
                 yield ("wait", f"vec_full[{g & 1}]", g >> 1)
                 yield ("wait", "x_full", g)
                 yield ("arrive", "x_free")
                 if g > 0:
                     yield ("wait", "acc_done", g - 1)
+                if g + 1 < total:
+                    yield ("arrive", f"vec_full[{(g + 1) & 1}]")   # the next tile's, a tile ahead
                 if i == 0 and j > 0:
                     yield ("arrive", self.dkv(j - 1)[0])      # stage dK / dV of the finished item
                 yield ("arrive", "w_full")
