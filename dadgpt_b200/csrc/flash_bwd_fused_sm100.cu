@@ -42,6 +42,7 @@ constexpr int kFCompute = 16 * 32;
 constexpr int kFStages = 2;
 constexpr int kFRing = 4;                 // entries of the work-item ring (a power of two)
 constexpr float kFLog2e = 1.4426950408889634f;
+constexpr int kVecBox = 132;   // fp32 words one row-scalar load brings in
 
 struct FusedSmem {
   static constexpr int kK = 0;                          // two buffers: items alternate
@@ -52,15 +53,20 @@ struct FusedSmem {
   static constexpr int kDS = kP + 2 * kFPanel;
   static constexpr int kDQ = kDS + 2 * kFPanel;         // [128 q][64] fp32, two 128-byte panels
   static constexpr int kBars = kDQ + 2 * kFPanel;
-  static constexpr int kVec = kBars + 256;              // 2 x [lse log2e | delta][128] fp32
-  static constexpr int kBytes = kVec + 2 * 2 * 128 * 4;
+  // Per-row scalars of a query tile, one buffer per Q / dO stage: lse and delta of kVecBox rows
+  // each (the tile's 128 and up to three before them: a TMA load starts on a 16-byte boundary),
+  // every vector on its own 128-byte boundary.
+  static constexpr int kVec = kBars + 256;
+  static constexpr int kVecDelta = 640, kVecStride = 1280;
+  static constexpr int kBytes = kVec + kFStages * kVecStride;
+  static_assert(kVec % 128 == 0 && kVecBox * 4 <= kVecDelta, "row-scalar buffers misplaced");
   static_assert(kBytes <= 232448, "shared memory budget of one CTA exceeded");
 };
 
 struct FusedBars {
   uint64_t kv_full[2], dkv_sent[2], q_full[kFStages], do_full[kFStages], qdo_empty[kFStages];
   uint64_t item_ready[kFRing], item_free[kFRing];
-  uint64_t x_full, x_free, w_full, acc_done, dq_drained, dq_staged, dq_sent, dkv_staged[2], vec_full[2];
+  uint64_t x_full, x_free, w_full, acc_done, dq_drained, dq_staged, dq_sent, dkv_staged[2], vec_full[kFStages];
   int ring[kFRing];
   uint32_t tmem_base;
   int abort_flag;
@@ -147,8 +153,9 @@ __global__ void __launch_bounds__(kFThreads, 1)
 flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                        const __grid_constant__ CUtensorMap map_dqw, const __grid_constant__ CUtensorMap map_dk,
-                       const __grid_constant__ CUtensorMap map_dv, const float* __restrict__ lse,
-                       const float* __restrict__ delta, int* __restrict__ item_counter, int BH, int S,
+                       const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CUtensorMap map_lse,
+                       const __grid_constant__ CUtensorMap map_delta, int lse_shift,
+                       int* __restrict__ item_counter, int BH, int S,
                        int heads, int group_bh, float scale, float rate, PhiloxKey rng, int64_t unit0,
                        const uint32_t* __restrict__ mask_bits, int* __restrict__ status) {
   using L = FusedSmem;
@@ -191,8 +198,7 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     mbar_init(&bars->dq_sent, 1);
     mbar_init(&bars->dkv_staged[0], kFCompute);
     mbar_init(&bars->dkv_staged[1], kFCompute);
-    mbar_init(&bars->vec_full[0], 128);
-    mbar_init(&bars->vec_full[1], 128);
+    for (int s = 0; s < kFStages; ++s) mbar_init(&bars->vec_full[s], 1);
     bars->abort_flag = 0;
     fence_mbar_init();
   }
@@ -214,6 +220,8 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       prefetch_tensormap(&map_k);
       prefetch_tensormap(&map_v);
       prefetch_tensormap(&map_do);
+      prefetch_tensormap(&map_lse);
+      prefetch_tensormap(&map_delta);
       int n_pub = 0;
       auto publish = [&](int item) -> bool {
         const int slot = n_pub & (kFRing - 1);
@@ -251,6 +259,13 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           tma_load_4d(smem + L::kQ + s * kFPanel, &map_q, &bars->q_full[s], 0, q0, uh, ub);
           mbar_arrive_expect_tx(&bars->do_full[s], kFPanel);
           tma_load_4d(smem + L::kDO + s * kFPanel, &map_do, &bars->do_full[s], 0, q0, uh, ub);
+          // The tile's row scalars ride the same ring: the stage is free once the GEMMs of the
+          // tile that used it have completed, and those followed the arithmetic that read the
+          // scalars. The load starts at the 16-byte boundary at or below the tile's first row.
+          const int at = t.bh * S + q0;
+          mbar_arrive_expect_tx(&bars->vec_full[s], 2 * kVecBox * 4);
+          tma_load_1d(smem + L::kVec + s * L::kVecStride, &map_lse, &bars->vec_full[s], (at + lse_shift) & ~3);
+          tma_load_1d(smem + L::kVec + s * L::kVecStride + L::kVecDelta, &map_delta, &bars->vec_full[s], at & ~3);
         }
         cur = nxt;
         nxt = after;
@@ -308,6 +323,9 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           mma_ss(tmem + kColDV, desc_at(p_t, kk * 2048), desc_at(dd, kk * 2048), idesc_t, acc);
           mma_ss(tmem + kColDK, desc_at(ds_t, kk * 2048), desc_at(qd, kk * 2048), idesc_t, acc);
         }
+        // Q and dO of this stage are last read by the products above: the stage goes back to the
+        // producer now, not after dQ, which only needs dS and K.
+        mma_commit(&bars->qdo_empty[s]);
         // the previous tile's dQ must have left tensor memory before this one overwrites it; the
         // compute warps read it right after they publish P / dS, while dV / dK are running
         if (g > 0 && !mbar_wait(&bars->dq_drained, (g - 1) & 1, abort_flag)) return false;
@@ -317,7 +335,6 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           mma_ss(tmem + kColDQ, desc_at(ds_k, (kk / 4) * kFPanel + (kk % 4) * 32),
                  desc_at(kd, kk * 2048), idesc_q, kk > 0 ? 1u : 0u);
         }
-        mma_commit(&bars->qdo_empty[s]);
         mma_commit(&bars->acc_done);
         return true;
       };
@@ -451,36 +468,9 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       fence_proxy_async_smem();
       mbar_arrive(&bars->dkv_staged[kb]);
     };
-    // Per-row scalars (lse log2e and delta of the tile's 128 queries). The four threads that
-    // share a row need the same two values; only the first of them (column group 0: 128 threads)
-    // loads them, one tile ahead, and hands them over through one of two shared-memory buffers:
-    // global loads of the compute warps queue behind the dQ reduce traffic on the SM's path to
-    // L2, so there should be few of them and none whose latency is exposed. The loaded words are
-    // therefore not touched before the tile after: an instruction that uses one (a scale, a
-    // select) would hold its warp, and through the tile's barriers all sixteen, until the load
-    // is back. Out-of-range rows load a valid address and are replaced when the values are
-    // published. Queries beyond S contribute nothing (p = exp2(-inf) = 0).
-    float* vec = reinterpret_cast<float*>(smem + L::kVec);
-    struct RowLoad { float lse, delta; bool in; };
-    auto load_row = [&](bool valid, int q_tile, int bh) -> RowLoad {
-      RowLoad r{0.f, 0.f, false};
-      if (cg != 0) return r;
-      const int qq = q_tile * kFT + row;
-      r.in = valid && qq < S;
-      const size_t at = r.in ? static_cast<size_t>(bh) * S + qq : 0;
-      r.lse = lse[at];
-      r.delta = delta[at];
-      return r;
-    };
-    // column group 0 publishes the scalars of tile g (buffer g % 2)
-    auto publish_row = [&](const RowLoad& r, int g) {
-      if (cg != 0) return;
-      float* vb = vec + (g & 1) * 256;
-      vb[row] = r.in ? r.lse * kFLog2e : INFINITY;
-      vb[128 + row] = r.in ? r.delta * scale : 0.f;
-      mbar_arrive(&bars->vec_full[g & 1]);
-    };
-
+    // Per-row scalars (lse and delta of the tile's 128 queries) come from the producer's loads:
+    // global loads of the compute warps would queue behind the dQ reduce traffic on the SM's
+    // path to L2, for thousands of clocks. Queries beyond S contribute nothing (p = exp2(-inf)).
     // Keep bits of this thread's 32 key columns for one tile: word cg of the row's record,
     // fetched a tile ahead like the row scalars.
     auto load_keep = [&](bool valid, int q_tile, int k_tile, int bh) -> uint32_t {
@@ -491,12 +481,10 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     ItemFeed feed{bars, abort_flag, 0};
     int cur = feed.fetch(n_items);
     int nxt = cur < n_items ? feed.fetch(n_items) : n_items;
-    RowLoad next_row{0.f, 0.f, false};
     uint32_t keep_word = 0u, next_keep = 0u;
-    if (cur < n_items) {
+    if (DROP == 2 && cur < n_items) {
       const Item t0 = decode_item(cur, BH, n_tiles, group_bh);
-      publish_row(load_row(true, t0.kt, t0.bh), 0);
-      if (DROP == 2) next_keep = load_keep(true, t0.kt, t0.kt, t0.bh);
+      next_keep = load_keep(true, t0.kt, t0.kt, t0.bh);
     }
     int g = 0, j = 0;
 
@@ -507,24 +495,25 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int q = (t.kt + i) * kFT + row;
         const bool diagonal = (i == 0);
         const bool new_item = (i == 0 && j > 0);  // the item before this one is complete
-        const float* vbuf = vec + (g & 1) * 256;
-        if (DROP == 2) keep_word = next_keep;
-        // the next tile's scalars and keep bits: requested here, first touched after this tile's
-        // arithmetic
-        const bool more = (i + 1 < t.n_it) || nxt < n_items;
-        if (i + 1 < t.n_it) {
-          next_row = load_row(true, t.kt + i + 1, t.bh);
-          if (DROP == 2) next_keep = load_keep(true, t.kt + i + 1, t.kt, t.bh);
-        } else {
-          const Item tn = decode_item(nxt < n_items ? nxt : 0, BH, n_tiles, group_bh);
-          next_row = load_row(nxt < n_items, tn.kt, tn.bh);
-          if (DROP == 2) next_keep = load_keep(nxt < n_items, tn.kt, tn.kt, tn.bh);
+        const int vs = g % kFStages;
+        const float* vbuf = reinterpret_cast<const float*>(smem + L::kVec + vs * L::kVecStride);
+        if (DROP == 2) {
+          // the next tile's keep bits: requested here, first used in that tile
+          keep_word = next_keep;
+          if (i + 1 < t.n_it) {
+            next_keep = load_keep(true, t.kt + i + 1, t.kt, t.bh);
+          } else {
+            const Item tn = decode_item(nxt < n_items ? nxt : 0, BH, n_tiles, group_bh);
+            next_keep = load_keep(nxt < n_items, tn.kt, tn.kt, tn.bh);
+          }
         }
-        // (one barrier per buffer: its next completion, for tile g+2, comes after the GEMMs of
-        // tile g have been seen complete, which need this thread's own P / dS of tile g, so the
-        // phase cannot run away from a slow waiter)
-        if (!(ok = mbar_wait(&bars->vec_full[g & 1], (g >> 1) & 1, abort_flag))) break;
-        const float row_lse2 = vbuf[row], row_delta_s = vbuf[128 + row];
+        // (one barrier per stage: its next completion needs the stage back from the GEMMs of tile
+        // g, hence this thread's own P / dS, so the phase cannot run away from a slow waiter)
+        if (!(ok = mbar_wait(&bars->vec_full[vs], (g / kFStages) & 1, abort_flag))) break;
+        const int at = t.bh * S + (t.kt + i) * kFT;     // the tile's first row in the [BH, S] vectors
+        const bool in = q < S;
+        const float row_lse2 = in ? vbuf[((at + lse_shift) & 3) + row] * kFLog2e : INFINITY;
+        const float row_delta_s = in ? vbuf[L::kVecDelta / 4 + (at & 3) + row] * scale : 0.f;
         if (!(ok = mbar_wait(&bars->x_full, g & 1, abort_flag))) break;
         tc_fence_after_sync();
         // Sixteen columns at a time: the packed results have to wait in registers for the P / dS
@@ -583,9 +572,6 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (!(ok = mbar_wait(&bars->acc_done, (g - 1) & 1, abort_flag))) break;
           tc_fence_after_sync();
         }
-        // Scalars of tile g+1 into the other buffer: it was last read in tile g-1, which every
-        // thread had finished before the GEMMs seen complete just above could start.
-        if (more) publish_row(next_row, g + 1);
         // Across an item boundary tile g-1 also completed dK / dV of the previous item: take them
         // out of tensor memory before w_full lets this item's first GEMMs overwrite them.
         if (new_item) stage_dkv((j - 1) & 1);
@@ -729,6 +715,33 @@ int make_dq_workspace_map(CUtensorMap* map, float* ws, int BH, int S) {
   return DADATTN_OK;
 }
 
+// A [n] fp32 vector of per-row scalars as a 1-D map with boxes of kVecBox words. `base` need not
+// be 16-byte aligned: the map starts at the boundary below it and *shift is the number of words
+// in between, which the kernel adds to its row index.
+int make_row_scalar_map(CUtensorMap* map, const float* base, int64_t n, int* shift) {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  if (!fn) return fail(DADATTN_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const uintptr_t addr = reinterpret_cast<uintptr_t>(base);
+  if (addr % 4) return fail(DADATTN_E_ARG, "a float vector is not 4-byte aligned");
+  *shift = static_cast<int>((addr % 16) / 4);
+  const cuuint64_t dims[1] = {static_cast<cuuint64_t>(n + *shift)};
+  const cuuint64_t strides[1] = {0};   // unused with one dimension
+  const cuuint32_t box[1] = {kVecBox};
+  const cuuint32_t estr[1] = {1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 1, reinterpret_cast<void*>(addr - addr % 16), dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(DADATTN_E_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return DADATTN_OK;
+}
+
 }  // namespace
 }  // namespace dadattn
 namespace dadattn {
@@ -754,7 +767,8 @@ int launch_bwd_fused_d64(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspa
   float* delta = static_cast<float*>(workspace);
   float* dq_ws = reinterpret_cast<float*>(static_cast<char*>(workspace) + delta_bytes);
   int* item_counter = reinterpret_cast<int*>(static_cast<char*>(workspace) + delta_bytes + dq_bytes);
-  CUtensorMap mq, mk, mv, mdo, mws, mdk, mdv;
+  CUtensorMap mq, mk, mv, mdo, mws, mdk, mdv, mlse, mdelta;
+  int lse_shift = 0, delta_shift = 0;   // the workspace is 256-byte aligned: delta needs none
   if (int rc = make_tensor_map_bf16_units(&mq, q, BH, S, kFD, kFT, lay)) return rc;
   if (int rc = make_tensor_map_bf16_units(&mk, k, BH, S, kFD, kFT, lay)) return rc;
   if (int rc = make_tensor_map_bf16_units(&mv, v, BH, S, kFD, kFT, lay)) return rc;
@@ -762,6 +776,13 @@ int launch_bwd_fused_d64(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspa
   if (int rc = make_tensor_map_bf16_units(&mdk, dk, BH, S, kFD, kFT, lay)) return rc;
   if (int rc = make_tensor_map_bf16_units(&mdv, dv, BH, S, kFD, kFT, lay)) return rc;
   if (int rc = make_dq_workspace_map(&mws, dq_ws, BH, S)) return rc;
+  // (the kernel indexes the [BH, S] vectors with 32-bit TMA coordinates)
+  if (static_cast<int64_t>(BH) * S > INT32_MAX - 1024)
+    return fail(DADATTN_E_UNSUPPORTED, "BH * S = %lld rows exceed what the fused backward addresses",
+                static_cast<long long>(BH) * S);
+  if (int rc = make_row_scalar_map(&mlse, lse, static_cast<int64_t>(BH) * S, &lse_shift)) return rc;
+  if (int rc = make_row_scalar_map(&mdelta, delta, static_cast<int64_t>(BH) * S, &delta_shift)) return rc;
+  if (delta_shift != 0) return fail(DADATTN_E_ARG, "the backward workspace is not 16-byte aligned");
   int* status = device_status_word();
   if (!status) return DADATTN_E_CUDA;
 
@@ -789,7 +810,7 @@ int launch_bwd_fused_d64(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspa
                          : flash_bwd_fused_kernel<0>;
   DAD_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FusedSmem::kBytes));
   DAD_CUDA(launch_pdl(kern, grid, dim3(kFThreads), FusedSmem::kBytes, st, mq, mk, mv, mdo, mws, mdk, mdv,
-                      lse, static_cast<const float*>(delta), item_counter, BH, S, lay.heads, group_bh, scale, rate,
+                      mlse, mdelta, lse_shift, item_counter, BH, S, lay.heads, group_bh, scale, rate,
                       rng, unit0, mask_bits, status));
   stage_event(2, st);
   const int64_t n8 = rows * kFD / 8;

@@ -129,6 +129,14 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// 1-D form, for vectors of per-row scalars. x times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_1d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x) {
+  asm volatile(
+      "cp.async.bulk.tensor.1d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x)
+      : "memory");
+}
+
 // 4-D form: (x, row, head, batch). The bf16 kernels address a (batch, head) unit this way so
 // that one code path serves both memory layouts (see UnitLayout below).
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,

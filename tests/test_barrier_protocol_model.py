@@ -71,6 +71,7 @@ class Sim:
                     yield ("wait", f"qdo_empty[{s}]", use - 1)
                 yield ("tma", f"q_full[{s}]")
                 yield ("tma", f"do_full[{s}]")
+                yield ("tma", f"vec_full[{s}]")           # the tile's row scalars ride the same ring
                 g += 1
 
     def issuer(self):
@@ -95,9 +96,9 @@ class Sim:
                     yield from issue_x(g + 1)
                 # issue_acc(g)
                 yield ("wait", "w_full", g)
+                yield ("commit", f"qdo_empty[{g % STAGES}]")     # after dV / dK, before dQ
                 if g > 0:
                     yield ("wait", "dq_drained", g - 1)
-                yield ("commit", f"qdo_empty[{g % STAGES}]")
                 yield ("commit", "acc_done")
                 g += 1
 
@@ -110,18 +111,13 @@ class Sim:
 
         g = 0
         j = 0
-        total = sum(self.items)
-        if total:
-            yield ("arrive", "vec_full[0]")               # the first tile's row scalars
         for j, n_it in enumerate(self.items):
             for i in range(n_it):
-                yield ("wait", f"vec_full[{g & 1}]", g >> 1)
+                yield ("wait", f"vec_full[{g % STAGES}]", g // STAGES)
                 yield ("wait", "x_full", g)
                 yield ("arrive", "x_free")
                 if g > 0:
                     yield ("wait", "acc_done", g - 1)
-                if g + 1 < total:
-                    yield ("arrive", f"vec_full[{(g + 1) & 1}]")   # the next tile's, a tile ahead
                 if i == 0 and j > 0:
                     yield ("arrive", self.dkv(j - 1)[0])      # stage dK / dV of the finished item
                 yield ("arrive", "w_full")
