@@ -19,9 +19,14 @@
 // operand are dS^T (resp. P^T) for dK (resp. dV). The Q / dO tiles are K-major A operands of the
 // score GEMMs and MN-major B operands of dK / dV; K is the K-major B operand of S and the
 // MN-major B operand of dQ.
-//   warp 0       TMA producer           warp 1       MMA issuer + TMEM owner
-//   warps 2-17   compute: four warps per TMEM lane quadrant, 32 of the 128 key columns each
-//   warp 18      dQ reducer: issues the TMA reduce-adds and recycles the two staging buffers
+//   warps 0-15   compute: four warps per TMEM lane quadrant, 32 of the 128 key columns each
+//   warp 16      TMA producer           warp 17      MMA issuer + TMEM owner
+//   warp 18      dQ reducer: issues the TMA reduce-adds and the dK / dV stores   (warp 19 idle)
+//   warps 20-23  accumulator drain: one thread per TMEM lane takes each tile's dQ, and each
+//                item's dK / dV, out of tensor memory into the shared-memory staging buffers,
+//                while the compute warps are already on the next tile's arithmetic
+// The roles are whole warpgroups so that registers can move between them (setmaxnreg): the
+// compute warps hold two packed tiles' worth of values and get 96 registers, the others 56 / 40.
 #include <cuda_bf16.h>
 
 #include <cfloat>
@@ -37,8 +42,18 @@ using namespace ptx;
 constexpr int kFT = 128;                  // tile edge: queries per step, keys per CTA
 constexpr int kFD = 64;                   // head size
 constexpr int kFPanel = 128 * 128;        // [128 rows][64 bf16] swizzled panel
-constexpr int kFThreads = 19 * 32;
+constexpr int kFThreads = 24 * 32;
 constexpr int kFCompute = 16 * 32;
+constexpr int kFDrain = 4 * 32;           // one thread per TMEM lane
+constexpr int kWarpProducer = 16, kWarpIssuer = 17, kWarpReducer = 18, kWarpDrain0 = 20;
+// Registers per thread after the warpgroups have rebalanced. The pool is what the CTA was launched
+// with (kRegsLaunch per thread, the most that 768 threads can have): an increase beyond it would
+// wait for ever.
+constexpr int kRegsLaunch = 80, kRegsCompute = 96, kRegsHelper = 56, kRegsDrain = 40;
+static_assert(kFCompute * kRegsCompute + 128 * kRegsHelper + kFDrain * kRegsDrain <= kFThreads * kRegsLaunch,
+              "the warpgroups ask for more registers than the CTA owns");
+static_assert(kFThreads * kRegsLaunch <= 65536 && (kRegsLaunch + 8) * kFThreads > 65536,
+              "kRegsLaunch is not what the compiler gives a CTA of this size");
 constexpr int kFStages = 2;
 constexpr int kFRing = 4;                 // entries of the work-item ring (a power of two)
 constexpr float kFLog2e = 1.4426950408889634f;
@@ -56,7 +71,8 @@ struct FusedSmem {
   // Per-row scalars of a query tile, one buffer per Q / dO stage: lse and delta of kVecBox rows
   // each (the tile's 128 and up to three before them: a TMA load starts on a 16-byte boundary),
   // every vector on its own 128-byte boundary.
-  static constexpr int kVec = kBars + 256;
+  static constexpr int kBarsBytes = 384;
+  static constexpr int kVec = kBars + kBarsBytes;
   static constexpr int kVecDelta = 640, kVecStride = 1280;
   static constexpr int kBytes = kVec + kFStages * kVecStride;
   static_assert(kVec % 128 == 0 && kVecBox * 4 <= kVecDelta, "row-scalar buffers misplaced");
@@ -67,10 +83,12 @@ struct FusedBars {
   uint64_t kv_full[2], dkv_sent[2], q_full[kFStages], do_full[kFStages], qdo_empty[kFStages];
   uint64_t item_ready[kFRing], item_free[kFRing];
   uint64_t x_full, x_free, w_full, acc_done, dq_drained, dq_staged, dq_sent, dkv_staged[2], vec_full[kFStages];
+  uint64_t dkv_drained;
   int ring[kFRing];
   uint32_t tmem_base;
   int abort_flag;
 };
+static_assert(sizeof(FusedBars) <= FusedSmem::kBarsBytes, "barriers overflow their shared-memory slot");
 
 // TMA reduce-add of one [128 rows][32 fp32] panel from shared memory into the dQ workspace.
 __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, const void* smem_src, int x,
@@ -187,22 +205,23 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     for (int s = 0; s < kFRing; ++s) {
       mbar_init(&bars->item_ready[s], 1);
-      mbar_init(&bars->item_free[s], kFCompute + 2);   // compute threads, MMA issuer, reducer
+      mbar_init(&bars->item_free[s], kFCompute + kFDrain + 2);   // compute, drain, MMA issuer, reducer
     }
     mbar_init(&bars->x_full, 1);
     mbar_init(&bars->x_free, kFCompute);
     mbar_init(&bars->w_full, kFCompute);
     mbar_init(&bars->acc_done, 1);
-    mbar_init(&bars->dq_drained, kFCompute);
-    mbar_init(&bars->dq_staged, kFCompute);
+    mbar_init(&bars->dq_drained, kFDrain);
+    mbar_init(&bars->dq_staged, kFDrain);
+    mbar_init(&bars->dkv_drained, kFDrain);
     mbar_init(&bars->dq_sent, 1);
-    mbar_init(&bars->dkv_staged[0], kFCompute);
-    mbar_init(&bars->dkv_staged[1], kFCompute);
+    mbar_init(&bars->dkv_staged[0], kFDrain);
+    mbar_init(&bars->dkv_staged[1], kFDrain);
     for (int s = 0; s < kFStages; ++s) mbar_init(&bars->vec_full[s], 1);
     bars->abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 1) {
+  if (warp == kWarpIssuer) {
     tmem_alloc(&bars->tmem_base, kTmemCols);
     tmem_relinquish();
   }
@@ -213,7 +232,11 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   pdl_wait();
   pdl_launch_dependents();
 
-  if (warp == 0) {
+  // Registers move from the helper warpgroups to the compute warpgroups; each branch below sets
+  // its own budget first.
+  if (warp >= kWarpProducer && warp < kWarpDrain0) {
+  setmaxnreg_dec<kRegsHelper>();
+  if (warp == kWarpProducer) {
     // ------------------------------ scheduler + TMA producer ------------------------------
     if (elect_one()) {
       prefetch_tensormap(&map_q);
@@ -271,7 +294,7 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         nxt = after;
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == kWarpIssuer) {
     // ------------------------------ MMA issuer ------------------------------
     if (elect_one()) {
       constexpr uint32_t idesc_x = make_idesc_bf16(128, 128, 0, 0);   // S, dP: both K-major
@@ -307,14 +330,16 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         return true;
       };
       // dV += P^T dO, dK += dS^T Q (fresh accumulators on an item's first tile), dQ_tile = dS K
-      auto issue_acc = [&](int g, int kb, bool first_of_item) -> bool {
+      auto issue_acc = [&](int g, int item, bool first_of_item) -> bool {
+        const int kb = item & 1;
         const int s = g % kFStages;
         const SmemDescBase qd{q0_desc.lo + s * (kFPanel >> 4), q0_desc.hi};
         const SmemDescBase dd{do0_desc.lo + s * (kFPanel >> 4), do0_desc.hi};
         const SmemDescBase kd{k0_desc.lo + kb * (kFPanel >> 4), k0_desc.hi};
-        // w_full also says that the compute warps have taken the previous item's dK / dV out of
-        // tensor memory
         if (!mbar_wait(&bars->w_full, g & 1, abort_flag)) return false;
+        // a new item's first products overwrite dV / dK: the drain warps must have taken the
+        // previous item's out of tensor memory
+        if (first_of_item && item > 0 && !mbar_wait(&bars->dkv_drained, (item - 1) & 1, abort_flag)) return false;
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < kFT / 16; ++kk) {   // K dimension = 128 queries, 16 per MMA
@@ -356,13 +381,13 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             ok = mbar_wait(&bars->x_free, g & 1, abort_flag) &&
                  mbar_wait(&bars->kv_full[kbn], ((j + 1) >> 1) & 1, abort_flag) && issue_x(g + 1, kbn);
           }
-          ok = ok && issue_acc(g, j & 1, i == 0);
+          ok = ok && issue_acc(g, j, i == 0);
         }
         cur = nxt;
         nxt = cur < n_items ? feed.fetch(n_items) : n_items;
       }
     }
-  } else if (warp == 18) {
+  } else if (warp == kWarpReducer) {
     // ------------------------------ dQ reducer / dK, dV writer ------------------------------
     if (elect_one()) {
       prefetch_tensormap(&map_dqw);
@@ -410,64 +435,89 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       bulk_wait0();   // every sum and store has landed before the CTA retires
     }
+  }
+  } else if (warp >= kWarpDrain0) {
+    // ------------------------------ accumulator drain warps ------------------------------
+    setmaxnreg_dec<kRegsDrain>();
+    const int quad = warp % 4;
+    const int row = quad * 32 + lane;     // TMEM lane = query row (dQ) or key row (dK / dV)
+    const uint32_t tlane = tmem + (static_cast<uint32_t>(quad * 32) << 16);
+    ItemFeed feed{bars, abort_flag, 0};
+    int cur = feed.fetch(n_items);
+    int nxt = cur < n_items ? feed.fetch(n_items) : n_items;
+    bool ok = true;
+    int g = 0;
+    for (int j = 0; ok && cur < n_items; ++j) {
+      const int n_it = decode_item(cur, BH, n_tiles, group_bh).n_it;
+      for (int i = 0; i < n_it; ++i, ++g) {
+        // the staging buffer back from the previous tile's reduce, then this tile's GEMMs
+        if (g > 0 && !(ok = mbar_wait(&bars->dq_sent, (g - 1) & 1, abort_flag))) break;
+        if (!(ok = mbar_wait(&bars->acc_done, g & 1, abort_flag))) break;
+        tc_fence_after_sync();
+        if (i + 1 == n_it) {
+          // The item is complete: dK / dV, tensor memory -> bf16 rows in the item's own K / V
+          // buffers (every GEMM that read them has completed), from where the reducer warp
+          // stores them. Sixteen columns at a time; dV is columns [0, 64), dK [64, 128).
+          const int kb = j & 1;
+#pragma unroll 1
+          for (int c = 0; c < 8; ++c) {
+            uint32_t o[16];
+            tmem_ld16(tlane + kColDV + c * 16, o);   // kColDK = kColDV + 64
+            tmem_wait_ld();
+            uint8_t* dst = smem + (c < 4 ? L::kV : L::kK) + kb * kFPanel + row * 128;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int chunk = (c & 3) * 2 + h;
+              *reinterpret_cast<uint4*>(dst + ((chunk ^ (row & 7)) << 4)) = make_uint4(
+                  pack_bf16(__uint_as_float(o[8 * h + 0]), __uint_as_float(o[8 * h + 1])),
+                  pack_bf16(__uint_as_float(o[8 * h + 2]), __uint_as_float(o[8 * h + 3])),
+                  pack_bf16(__uint_as_float(o[8 * h + 4]), __uint_as_float(o[8 * h + 5])),
+                  pack_bf16(__uint_as_float(o[8 * h + 6]), __uint_as_float(o[8 * h + 7])));
+            }
+          }
+          tc_fence_before_sync();
+          mbar_arrive(&bars->dkv_drained);          // the next item's products may overwrite dV / dK
+          fence_proxy_async_smem();
+          mbar_arrive(&bars->dkv_staged[kb]);
+        }
+        // dQ of the tile: tensor memory -> swizzled fp32 staging ([2 panels][128 rows][32 fp32]),
+        // which the reducer warp sends on
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[16];
+          tmem_ld16(tlane + kColDQ + c * 16, o);
+          tmem_wait_ld();
+          if (c == 3) {
+            tc_fence_before_sync();
+            mbar_arrive(&bars->dq_drained);          // the next tile's dQ may overwrite this one
+          }
+          uint8_t* dq_row = smem + L::kDQ + (c / 2) * kFPanel + row * 128;
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
+            const int chunk = (c & 1) * 4 + c4;
+            *reinterpret_cast<uint4*>(dq_row + ((chunk ^ (row & 7)) << 4)) =
+                make_uint4(o[4 * c4], o[4 * c4 + 1], o[4 * c4 + 2], o[4 * c4 + 3]);
+          }
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&bars->dq_staged);
+      }
+      cur = nxt;
+      nxt = (ok && cur < n_items) ? feed.fetch(n_items) : n_items;
+    }
   } else {
     // ------------------------------ compute warps ------------------------------
-    const int cw = warp - 2;              // 0..15
+    setmaxnreg_inc<kRegsCompute>();
     const int quad = warp % 4;            // TMEM lane quadrant of this warp
-    const int cg = cw / 4;                // which 32 key columns of the 128 (and 16 dQ columns)
+    const int cg = warp / 4;              // which 32 key columns of the 128
     const int row = quad * 32 + lane;     // query row within the tile = TMEM lane
     const uint32_t tlane = tmem + (static_cast<uint32_t>(quad * 32) << 16);
     const float scale_log2 = scale * kFLog2e;
     const float keep_scale = DROP ? 1.0f / (1.0f - rate) : 1.0f;
     uint8_t* p_row = smem + L::kP + (cg / 2) * kFPanel + row * 128;
     uint8_t* ds_row = smem + L::kDS + (cg / 2) * kFPanel + row * 128;
-    uint8_t* dq_row = smem + L::kDQ + (cg / 2) * kFPanel + row * 128;
     bool ok = true;
 
-    // dQ of tile t: TMEM -> swizzled fp32 staging, which the reducer warp sends on. The caller
-    // has seen acc_done of tile t.
-    auto drain_dq = [&](int t) -> bool {
-      uint32_t o[16];
-      tmem_ld16(tlane + kColDQ + cg * 16, o);
-      tmem_wait_ld();
-      tc_fence_before_sync();
-      mbar_arrive(&bars->dq_drained);
-      // the reduce of the previous tile must have finished reading the staging buffer
-      if (t > 0 && !mbar_wait(&bars->dq_sent, (t - 1) & 1, abort_flag)) return false;
-#pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        const int chunk = (cg & 1) * 4 + c4;
-        *reinterpret_cast<uint4*>(dq_row + ((chunk ^ (row & 7)) << 4)) =
-            make_uint4(o[4 * c4], o[4 * c4 + 1], o[4 * c4 + 2], o[4 * c4 + 3]);
-      }
-      fence_proxy_async_smem();
-      mbar_arrive(&bars->dq_staged);
-      return true;
-    };
-    // dK / dV of a finished item: tensor memory -> bf16 rows in the item's own K / V buffers
-    // (every GEMM that read them has completed), from where the reducer warp stores them. cg 0,1
-    // hold dV columns [32 (cg & 1), +32), cg 2,3 dK likewise; sixteen columns at a time.
-    auto stage_dkv = [&](int kb) {
-      uint8_t* dst = smem + (cg < 2 ? L::kV : L::kK) + kb * kFPanel + row * 128;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t o[16];
-        tmem_ld16(tlane + (cg < 2 ? kColDV : kColDK) + (cg & 1) * 32 + h * 16, o);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int chunk = (cg & 1) * 4 + h * 2 + i;
-          *reinterpret_cast<uint4*>(dst + ((chunk ^ (row & 7)) << 4)) = make_uint4(
-              pack_bf16(__uint_as_float(o[8 * i + 0]), __uint_as_float(o[8 * i + 1])),
-              pack_bf16(__uint_as_float(o[8 * i + 2]), __uint_as_float(o[8 * i + 3])),
-              pack_bf16(__uint_as_float(o[8 * i + 4]), __uint_as_float(o[8 * i + 5])),
-              pack_bf16(__uint_as_float(o[8 * i + 6]), __uint_as_float(o[8 * i + 7])));
-        }
-      }
-      tc_fence_before_sync();
-      fence_proxy_async_smem();
-      mbar_arrive(&bars->dkv_staged[kb]);
-    };
     // Per-row scalars (lse and delta of the tile's 128 queries) come from the producer's loads:
     // global loads of the compute warps would queue behind the dQ reduce traffic on the SM's
     // path to L2, for thousands of clocks. Queries beyond S contribute nothing (p = exp2(-inf)).
@@ -494,7 +544,6 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       for (int i = 0; i < t.n_it; ++i, ++g) {
         const int q = (t.kt + i) * kFT + row;
         const bool diagonal = (i == 0);
-        const bool new_item = (i == 0 && j > 0);  // the item before this one is complete
         const int vs = g % kFStages;
         const float* vbuf = reinterpret_cast<const float*>(smem + L::kVec + vs * L::kVecStride);
         if (DROP == 2) {
@@ -572,9 +621,6 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (!(ok = mbar_wait(&bars->acc_done, (g - 1) & 1, abort_flag))) break;
           tc_fence_after_sync();
         }
-        // Across an item boundary tile g-1 also completed dK / dV of the previous item: take them
-        // out of tensor memory before w_full lets this item's first GEMMs overwrite them.
-        if (new_item) stage_dkv((j - 1) & 1);
 #pragma unroll
         for (int v4 = 0; v4 < 4; ++v4) {
           const int chunk = (cg & 1) * 4 + v4;  // 16-byte chunk within the 128-byte row of the panel
@@ -586,26 +632,16 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         fence_proxy_async_smem();
         mbar_arrive(&bars->w_full);
-        if (g > 0 && !(ok = drain_dq(g - 1))) break;
       }
       cur = nxt;
       nxt = (ok && cur < n_items) ? feed.fetch(n_items) : n_items;
     }
 
-    // the last item's dK / dV and its last tile's dQ
-    if (ok && g > 0) {
-      ok = mbar_wait(&bars->acc_done, (g - 1) & 1, abort_flag);
-      tc_fence_after_sync();
-      if (ok) {
-        stage_dkv((j - 1) & 1);
-        ok = drain_dq(g - 1);
-      }
-    }
   }
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == kWarpIssuer) {
     __syncwarp();
     tc_fence_after_sync();
     tmem_dealloc(tmem, kTmemCols);

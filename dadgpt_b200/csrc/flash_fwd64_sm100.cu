@@ -104,25 +104,6 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       : "memory");
 }
 
-// 2^x for two values on the FMA pipe: integer part through the float-rounding trick, fraction
-// in [-0.5, 0.5] through a cubic (relative error 6e-4, below bf16's half ulp of 2e-3).
-// Arguments below -125 (masked scores are -inf) give exactly 0, as ex2.approx.ftz does.
-__device__ __forceinline__ float2 ex2_poly2(float2 x0) {
-  const float2 x = make_float2(fmaxf(x0.x, -125.f), fmaxf(x0.y, -125.f));
-  const float2 big = make_float2(12582912.f, 12582912.f);  // 1.5 * 2^23
-  const float2 t = fadd2(x, big);
-  const float2 f = fadd2(x, make_float2(big.x - t.x, big.y - t.y));
-  float2 p = ffma2(f, make_float2(0.0555041087f, 0.0555041087f), make_float2(0.2402265070f, 0.2402265070f));
-  p = ffma2(p, f, make_float2(0.6931471806f, 0.6931471806f));
-  p = ffma2(p, f, make_float2(1.0f, 1.0f));
-  float2 r;
-  r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
-  r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
-  if (x0.x < -125.f) r.x = 0.f;
-  if (x0.y < -125.f) r.y = 0.f;
-  return r;
-}
-
 // ---- work items --------------------------------------------------------------------------------
 // Item e (0 = heaviest): query-tile pair p = n_pairs - 1 - e / BH of (batch, head) e % BH.
 // CTA c of G takes, in order, the items k * G + (k even ? c : G - 1 - c): a serpentine deal of

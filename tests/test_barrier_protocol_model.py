@@ -2,8 +2,8 @@
 (dadgpt_b200/csrc/flash_bwd_fused_sm100.cu) and of the head-size-64 forward kernel
 (dadgpt_b200/csrc/flash_fwd64_sm100.cu), run under adversarial schedules.
 
-The kernel's roles (TMA producer, MMA issuer, the compute warps taken as one agent, the dQ reducer)
-are written down as the sequences of waits and arrivals they execute, per work item and tile, in
+The kernel's roles (TMA producer, MMA issuer, the compute warps and the accumulator drain warps
+each taken as one agent, the dQ reducer) are written down as the sequences of waits and arrivals they execute, per work item and tile, in
 the order of the CUDA source. Barriers behave like mbarriers waited by PARITY: a wait for the
 k-th completion passes iff the number of completed phases is odd/even as k + 1 is, so it is only
 correct while that number is k (blocks) or k + 1 (passes). The model checks, at every evaluation
@@ -16,9 +16,10 @@ arbitrary delays but in issue order; which runnable agent moves next is chosen a
 one agent at a time slowed down heavily. Item lists include the shapes that matter: single-tile
 items behind longer ones.
 
-With one `dkv_staged` barrier for all items (the layout the kernel had first) the model finds
-the violation that showed up as intermittent timeouts on some GPUs; with one barrier per K/V
-buffer (the committed layout) no schedule produces one.
+With one `dkv_staged` barrier for all items, and the compute warps draining the accumulators
+themselves (the layout the kernel had first), the model finds the violation that showed up as
+intermittent timeouts on some GPUs; with one barrier per K/V buffer no schedule produces one, in
+that role split or in the committed one (separate drain warps).
 """
 import random
 
@@ -32,8 +33,11 @@ class Violation(Exception):
 
 
 class Sim:
-    def __init__(self, items, per_buffer_dkv, rng):
+    def __init__(self, items, per_buffer_dkv, rng, drain_warps=True):
         self.items, self.per_buffer, self.rng = items, per_buffer_dkv, rng
+        # drain_warps=False: the kernel's earlier role split, in which the compute warps took
+        # dQ / dK / dV out of tensor memory themselves (kept to show what the model catches)
+        self.drain_warps = drain_warps
         self.done = {}          # barrier name -> completed phases
         self.count = {}         # barrier name -> arrivals in the current phase
         self.need = {}          # barrier name -> arrivals per phase (default 1)
@@ -96,6 +100,8 @@ class Sim:
                     yield from issue_x(g + 1)
                 # issue_acc(g)
                 yield ("wait", "w_full", g)
+                if i == 0 and j > 0 and self.drain_warps:
+                    yield ("wait", "dkv_drained", j - 1)
                 yield ("commit", f"qdo_empty[{g % STAGES}]")     # after dV / dK, before dQ
                 if g > 0:
                     yield ("wait", "dq_drained", g - 1)
@@ -103,6 +109,19 @@ class Sim:
                 g += 1
 
     def compute(self):
+        g = 0
+        for j, n_it in enumerate(self.items):
+            for i in range(n_it):
+                yield ("wait", f"vec_full[{g % STAGES}]", g // STAGES)
+                yield ("wait", "x_full", g)
+                yield ("arrive", "x_free")
+                if g > 0:
+                    yield ("wait", "acc_done", g - 1)
+                yield ("arrive", "w_full")
+                g += 1
+
+    def compute_and_drain(self):
+        """The earlier role split: the compute warps drain the accumulators between tiles."""
         def drain_dq(t):
             yield ("arrive", "dq_drained")
             if t > 0:
@@ -129,6 +148,21 @@ class Sim:
             yield ("arrive", self.dkv(j)[0])
             yield from drain_dq(g - 1)
 
+    def drain(self):
+        """The accumulator drain warps: each tile's dQ, each finished item's dK / dV."""
+        g = 0
+        for j, n_it in enumerate(self.items):
+            for i in range(n_it):
+                if g > 0:
+                    yield ("wait", "dq_sent", g - 1)
+                yield ("wait", "acc_done", g)
+                if i + 1 == n_it:
+                    yield ("arrive", "dkv_drained")
+                    yield ("arrive", self.dkv(j)[0])
+                yield ("arrive", "dq_drained")
+                yield ("arrive", "dq_staged")
+                g += 1
+
     def reducer(self):
         g = 0
         for j, n_it in enumerate(self.items):
@@ -144,8 +178,11 @@ class Sim:
                 g += 1
 
     def roles(self):
+        if not self.drain_warps:
+            return {"producer": self.producer(), "issuer": self.issuer(),
+                    "compute": self.compute_and_drain(), "reducer": self.reducer()}
         return {"producer": self.producer(), "issuer": self.issuer(), "compute": self.compute(),
-                "reducer": self.reducer()}
+                "drain": self.drain(), "reducer": self.reducer()}
 
     # ---- scheduler ----
     def run(self, max_steps=400000):
@@ -206,11 +243,11 @@ ITEM_LISTS = [
 ]
 
 
-def first_violation(per_buffer, seeds=range(300)):
+def first_violation(per_buffer, seeds=range(300), drain_warps=True):
     for items in ITEM_LISTS:
         for seed in seeds:
             try:
-                Sim(items, per_buffer, random.Random(seed)).run()
+                Sim(items, per_buffer, random.Random(seed), drain_warps).run()
             except Violation as e:
                 return items, seed, str(e)
     return None
@@ -220,8 +257,14 @@ def test_one_dkv_staged_barrier_per_buffer_survives_every_schedule():
     assert first_violation(per_buffer=True) is None
 
 
+def test_the_earlier_role_split_survives_too():
+    assert first_violation(per_buffer=True, drain_warps=False) is None
+
+
 def test_a_single_dkv_staged_barrier_is_caught():
-    found = first_violation(per_buffer=False)
+    # the failure belonged to the earlier role split: there the compute warps could stage the
+    # next item's dK / dV without needing the reducer
+    found = first_violation(per_buffer=False, drain_warps=False)
     assert found is not None, "the model no longer reproduces the double-advancing barrier"
     assert "dkv_staged" in found[2] or "deadlock" in found[2]
 
