@@ -258,13 +258,9 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       };
       // the first item is the CTA's own index; the counter hands out the rest
       int cur = static_cast<int>(blockIdx.x);
-      int nxt = static_cast<int>(gridDim.x) + atomicAdd(item_counter, 1);
       bool ok = publish(cur);
       int g = 0;
       for (int j = 0; ok && cur < n_items; ++j) {
-        // publish the following item (or the end mark) now: the other roles look one item ahead
-        ok = publish(nxt);
-        const int after = nxt < n_items ? static_cast<int>(gridDim.x) + atomicAdd(item_counter, 1) : nxt;
         const Item t = decode_item(cur, BH, n_tiles, group_bh);
         // K / V go to the buffer of the item before last, once its dK / dV have left that buffer
         const int kb = j & 1;
@@ -274,7 +270,12 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         mbar_arrive_expect_tx(&bars->kv_full[kb], 2 * kFPanel);
         tma_load_4d(smem + L::kK + kb * kFPanel, &map_k, &bars->kv_full[kb], 0, t.kt * kFT, uh, ub);
         tma_load_4d(smem + L::kV + kb * kFPanel, &map_v, &bars->kv_full[kb], 0, t.kt * kFT, uh, ub);
-        for (int i = 0; i < t.n_it; ++i, ++g) {
+        // The following item (or the end mark) is claimed only now, and published at once: the
+        // other roles look one item ahead. Every item a CTA holds in advance is work that no idle
+        // CTA can take near the end of the kernel, so it holds as few as it can.
+        const int nxt = static_cast<int>(gridDim.x) + atomicAdd(item_counter, 1);
+        ok = publish(nxt);
+        for (int i = 0; ok && i < t.n_it; ++i, ++g) {
           const int s = g % kFStages, use = g / kFStages;
           if (use > 0 && !(ok = mbar_wait(&bars->qdo_empty[s], (use - 1) & 1, abort_flag))) break;
           const int q0 = (t.kt + i) * kFT;
@@ -291,7 +292,6 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           tma_load_1d(smem + L::kVec + s * L::kVecStride + L::kVecDelta, &map_delta, &bars->vec_full[s], at & ~3);
         }
         cur = nxt;
-        nxt = after;
       }
     }
   } else if (warp == kWarpIssuer) {
