@@ -47,6 +47,7 @@
 #include <cuda_bf16.h>
 
 #include <cfloat>
+#include <vector>
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -106,16 +107,33 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 
 // ---- work items --------------------------------------------------------------------------------
 // Item e (0 = heaviest): query-tile pair p = n_pairs - 1 - e / BH of (batch, head) e % BH.
-// CTA c of G takes, in order, the items k * G + (k even ? c : G - 1 - c): a serpentine deal of
-// the weight-sorted list, so that a CTA that got an early (heavy) item in one row gets a late
-// (light) one in the next. Every role computes the same list; nothing is shared or reset.
+// Which items a CTA takes, in order, is fixed before the launch; every role computes the same
+// list, nothing is shared or reset. For small launches the host deals the weight-sorted list out
+// greedily (each item to the CTA with the least work so far) and passes the result as a kernel
+// parameter: entry k * G + c is the k-th item of CTA c. With only a handful of items per CTA the
+// closed-form deal below can leave some CTAs two K/V steps (of about 26) behind the others.
+// Larger launches use the closed form: CTA c of G takes the items k * G + (k even ? c : G-1-c), a
+// serpentine deal, so that a CTA that got an early (heavy) item in one row gets a late (light)
+// one in the next.
+constexpr int kDealEntries = 1536;
+constexpr uint16_t kDealNone = 0xffffu;
+struct F64Deal {
+  int rows;                      // 0: closed-form deal
+  uint16_t item[kDealEntries];
+};
 struct F64Item {
   int bh, qa, n_a, n_b, n_kv;   // n_b = 0 when the pair's second tile lies beyond the sequence
   bool valid;
 };
-__device__ __forceinline__ F64Item f64_item(int k, int BH, int n_tiles, int n_items) {
+__device__ __forceinline__ F64Item f64_item(const F64Deal& deal, int k, int BH, int n_tiles, int n_items) {
   const int G = static_cast<int>(gridDim.x), c = static_cast<int>(blockIdx.x);
-  const int e = k * G + ((k & 1) ? (G - 1 - c) : c);
+  int e;
+  if (deal.rows > 0) {
+    const uint16_t t = k < deal.rows ? deal.item[k * G + c] : kDealNone;
+    e = t == kDealNone ? n_items : t;
+  } else {
+    e = k * G + ((k & 1) ? (G - 1 - c) : c);
+  }
   F64Item it;
   it.valid = e < n_items;
   const int row = e / BH;
@@ -135,7 +153,7 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                    const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                    float* __restrict__ lse, int BH, int S, UnitLayout lay, float scale, float rate,
                    PhiloxKey rng, int64_t unit0, const uint4* __restrict__ mask_bits,
-                   int* __restrict__ status) {
+                   int* __restrict__ status, const __grid_constant__ F64Deal deal) {
   using L = F64Smem;
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kColS = 0, kColO = 256;   // score buffer (X,b) at 128 X + 64 b, O_(X,h) at kColO + 64 (2 X + h)
@@ -197,7 +215,7 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       int g = 0;  // K/V tiles loaded so far, over all items
       bool ok = true;
       for (int k = 0; ok; ++k) {
-        const F64Item it = f64_item(k, BH, n_tiles, n_items);
+        const F64Item it = f64_item(deal, k, BH, n_tiles, n_items);
         if (!it.valid) break;
         const int qb = k & 1;
         // the Q buffer frees when the last score product of the item before last has completed
@@ -270,8 +288,8 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       };
       auto n_of = [&](const F64Item& it) { return X ? it.n_b : it.n_a; };
 
-      F64Item cur = f64_item(0, BH, n_tiles, n_items);
-      F64Item nxt = f64_item(1, BH, n_tiles, n_items);
+      F64Item cur = f64_item(deal, 0, BH, n_tiles, n_items);
+      F64Item nxt = f64_item(deal, 1, BH, n_tiles, n_items);
       int g = 0;
       if (cur.valid) {
         ok = mbar_wait(&bars->q_full[0], 0, abort_flag) && mbar_wait(&bars->k_full[0], 0, abort_flag);
@@ -337,7 +355,7 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         if (n_x > 0) ++n_done;
         cur = nxt;
-        nxt = f64_item(k + 2, BH, n_tiles, n_items);
+        nxt = f64_item(deal, k + 2, BH, n_tiles, n_items);
       }
     }
   } else {
@@ -355,7 +373,7 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     bool ok = true;
 
     for (int k = 0; ok; ++k) {
-      const F64Item it = f64_item(k, BH, n_tiles, n_items);
+      const F64Item it = f64_item(deal, k, BH, n_tiles, n_items);
       if (!it.valid) break;
       const int n_x = X ? it.n_b : it.n_a;
       if (n_x == 0) continue;               // the pair's second tile lies beyond the sequence
@@ -523,6 +541,43 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   if (threadIdx.x == 0 && bars->abort_flag) report_timeout(status, bars->abort_flag);
 }
 
+// The greedy deal for a launch of G CTAs, or rows = 0 when the closed form serves (too many
+// items for the table). An item's weight is its K/V steps plus a half for its prologue and
+// epilogue. The last deal is kept: a training loop asks for the same one again and again.
+const F64Deal& fwd64_deal(int BH, int n_tiles, int G) {
+  struct Cached {
+    int BH = -1, n_tiles = -1, G = -1;
+    F64Deal deal;
+  };
+  static thread_local Cached cache;
+  if (cache.BH == BH && cache.n_tiles == n_tiles && cache.G == G) return cache.deal;
+  cache.BH = BH, cache.n_tiles = n_tiles, cache.G = G;
+  F64Deal& d = cache.deal;
+  d.rows = 0;
+  const int n_pairs = (n_tiles + 1) / 2;
+  const long long n_items = static_cast<long long>(BH) * n_pairs;
+  if (n_items > kDealEntries || G <= 0) return d;   // (every item takes an entry: no table could hold them)
+  std::vector<int> load(G, 0), count(G, 0);
+  std::vector<std::vector<uint16_t>> list(G);
+  // G is at most a few hundred and the table small: a linear scan for the least loaded CTA
+  for (int e = 0; e < static_cast<int>(n_items); ++e) {
+    const int qa = 2 * (n_pairs - 1 - e / BH);
+    const int n_kv = (qa + 1 < n_tiles) ? qa + 2 : qa + 1;
+    int best = 0;
+    for (int c = 1; c < G; ++c)
+      if (load[c] < load[best]) best = c;
+    load[best] += 2 * n_kv + 1;
+    list[best].push_back(static_cast<uint16_t>(e));
+  }
+  size_t rows = 0;
+  for (int c = 0; c < G; ++c) rows = list[c].size() > rows ? list[c].size() : rows;
+  if (rows * G > kDealEntries) return d;
+  for (size_t k = 0; k < rows; ++k)
+    for (int c = 0; c < G; ++c) d.item[k * G + c] = k < list[c].size() ? list[c][k] : kDealNone;
+  d.rows = static_cast<int>(rows);
+  return d;
+}
+
 template <int DROP>
 int launch_fwd64(uint16_t* out, float* lse, const uint16_t* q, const uint16_t* k, const uint16_t* v,
                  int BH, int S, const UnitLayout& lay, float scale, float rate, uint64_t seed,
@@ -544,7 +599,8 @@ int launch_fwd64(uint16_t* out, float* lse, const uint16_t* q, const uint16_t* k
   dim3 grid(static_cast<unsigned>(n_items < sms ? n_items : sms));
   DAD_CUDA(launch_pdl(kern, grid, dim3(kFwd64Threads), F64Smem::kBytes, st, mq, mk, mv,
                       reinterpret_cast<__nv_bfloat16*>(out), lse, BH, S, lay, scale, rate,
-                      make_philox(seed, offset), unit0, reinterpret_cast<const uint4*>(mask_bits), status));
+                      make_philox(seed, offset), unit0, reinterpret_cast<const uint4*>(mask_bits), status,
+                      fwd64_deal(BH, n_tiles, static_cast<int>(grid.x))));
   return DADATTN_OK;
 }
 
