@@ -21,13 +21,15 @@
 // exponentials of the current one are computed; at D = 64 two CTAs share an SM, at D = 128 the
 // scores are double-buffered in TMEM instead.
 //
+// The kernel template takes head sizes 64 and 128; the library instantiates it for 128 only: head
+// size 64 is served by the persistent two-tile kernel of flash_fwd64_sm100.cu.
+//
 // Every mbarrier wait is bounded (sm100_ptx.cuh). If one runs out, the CTA raises its abort
 // flag, everybody falls through to the common exit, TMEM is freed, and DADATTN_E_TIMEOUT is
 // left in the device status word.
 #include <cuda_bf16.h>
 
 #include <cfloat>
-#include <cstdlib>
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -537,13 +539,8 @@ extern "C" int dadattn_flash_fwd_bf16(uint16_t* out, float* lse, const uint16_t*
     return fail(DADATTN_E_ARG, "bf16 tensors must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool drop = rate > 0.f;
-  if (D == 64) {
-    static const bool old_kernel = getenv("DADATTN_FWD64_OLD") != nullptr;
-    if (!old_kernel)
-      return launch_fwd_bf16_d64(out, lse, q, k, v, BH, S, scale, rate, seed, offset, unit0, nullptr, 0, st);
-    return drop ? launch_fwd_bf16<64, true>(out, lse, q, k, v, BH, S, scale, rate, seed, offset, unit0, st)
-                : launch_fwd_bf16<64, false>(out, lse, q, k, v, BH, S, scale, 0.f, 0, 0, 0, st);
-  }
+  if (D == 64)   // head size 64 has a kernel of its own (flash_fwd64_sm100.cu)
+    return launch_fwd_bf16_d64(out, lse, q, k, v, BH, S, scale, rate, seed, offset, unit0, nullptr, 0, st);
   return drop ? launch_fwd_bf16<128, true>(out, lse, q, k, v, BH, S, scale, rate, seed, offset, unit0, st)
               : launch_fwd_bf16<128, false>(out, lse, q, k, v, BH, S, scale, 0.f, 0, 0, 0, st);
 }
