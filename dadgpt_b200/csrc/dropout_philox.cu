@@ -87,7 +87,10 @@ dropout_mask_bits_kernel(uint32_t* __restrict__ bits, int S, int n_tiles, float 
   while ((qt + 1) * (qt + 2) / 2 <= idx) ++qt;
   const int kt = idx - qt * (qt + 1) / 2;
   const int bh = static_cast<int>(blockIdx.y);
-  const int row = threadIdx.x >> 2, w = threadIdx.x & 3;
+  // A warp takes one 32-key word of 32 consecutive rows: on a diagonal tile the 32 x 32 blocks
+  // above the diagonal then cost nothing (a warp whose lanes mix words always has a lane with a
+  // full word to draw).
+  const int row = ((threadIdx.x >> 5) & 3) * 32 + (threadIdx.x & 31), w = threadIdx.x >> 7;
   const int q = qt * kMaskTile + row;
   const int key0 = kt * kMaskTile + w * 32;
   uint32_t word = 0;
