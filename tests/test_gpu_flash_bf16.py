@@ -283,3 +283,22 @@ def test_forward_many_single_tile_units(cuda, oracle):
     o32, l32 = torch.empty(BH, S, D, device=cuda), torch.empty(BH, S, device=cuda)
     dad.gpu_flash_attention_forward(o32, l32, tq.float(), tk.float(), tv.float(), BH, S, D, scale)
     assert (out.float() - o32).abs().max().item() <= 2e-2 and (lse - l32).abs().max().item() <= 1e-2
+
+
+@pytest.mark.parametrize("BH,S", [(1700, 128), (330, 640), (90, 1100)])
+def test_forward_work_item_deals_cover_every_item_once(cuda, BH, S):
+    """The head-size-64 forward hands its work items out before the launch: a greedy deal passed
+    as a kernel parameter for small launches (the last two shapes), a closed-form deal for large
+    ones (the first has more items than the table holds). Outputs start as NaN, so an item that
+    no CTA took shows; every unit is compared with the fp32 kernel."""
+    D, scale = 64, 0.125
+    g = torch.Generator(device="cpu").manual_seed(BH + S)
+    tq, tk, tv = ((torch.randn(BH, S, D, generator=g) * 0.7).to(cuda).to(torch.bfloat16) for _ in range(3))
+    out, lse = torch.full_like(tq, float("nan")), torch.full((BH, S), float("nan"), device=cuda)
+    dad.gpu_flash_attention_forward_bf16(out, lse, tq, tk, tv, BH, S, D, scale)
+    assert device_status() == 0
+    assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+    o32, l32 = torch.empty(BH, S, D, device=cuda), torch.empty(BH, S, device=cuda)
+    dad.gpu_flash_attention_forward(o32, l32, tq.float(), tk.float(), tv.float(), BH, S, D, scale)
+    assert (out.float() - o32).abs().max().item() <= 2e-2 and (lse - l32).abs().max().item() <= 1e-2
+
