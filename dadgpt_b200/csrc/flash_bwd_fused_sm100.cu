@@ -91,12 +91,21 @@ struct FusedBars {
 static_assert(sizeof(FusedBars) <= FusedSmem::kBarsBytes, "barriers overflow their shared-memory slot");
 
 // TMA reduce-add of one [128 rows][32 fp32] panel from shared memory into the dQ workspace.
+// `policy`: an L2 eviction policy (l2_policy_evict_last): the workspace is summed into up to
+// T / 128 times and read once more by the rounding pass, so its lines should outlive the streamed
+// Q / dO / K / V tiles in L2.
 __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, const void* smem_src, int x,
-                                                  int y, int z) {
+                                                  int y, int z, uint64_t policy) {
   asm volatile(
-      "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
-      ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+      "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group.L2::cache_hint "
+      "[%0, {%2, %3, %4}], [%1], %5;"
+      ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z), "l"(policy)
       : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
 }
 // TMA store of one [128 rows][64 bf16] swizzled panel from shared memory to (x, row, head, batch)
 // of a tensor in either memory layout (UnitLayout); rows beyond the sequence are dropped.
@@ -391,6 +400,7 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // ------------------------------ dQ reducer / dK, dV writer ------------------------------
     if (elect_one()) {
       prefetch_tensormap(&map_dqw);
+      const uint64_t keep = l2_policy_evict_last();
       prefetch_tensormap(&map_dk);
       prefetch_tensormap(&map_dv);
       ItemFeed feed{bars, abort_flag, 0};
@@ -403,8 +413,8 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int i = 0; ok && i < t.n_it; ++i, ++g) {
           if (!(ok = mbar_wait(&bars->dq_staged, g & 1, abort_flag))) break;
           const int q0 = (t.kt + i) * kFT;
-          tma_reduce_add_3d(&map_dqw, smem + L::kDQ, 0, q0, t.bh);
-          tma_reduce_add_3d(&map_dqw, smem + L::kDQ + kFPanel, 32, q0, t.bh);
+          tma_reduce_add_3d(&map_dqw, smem + L::kDQ, 0, q0, t.bh, keep);
+          tma_reduce_add_3d(&map_dqw, smem + L::kDQ + kFPanel, 32, q0, t.bh, keep);
           bulk_commit();
           if (i + 1 < t.n_it) {
             bulk_wait_read0();
