@@ -855,6 +855,19 @@ int launch_bwd_fused_d64(uint16_t* dq, uint16_t* dk, uint16_t* dv, void* workspa
   auto kern = rate > 0.f ? (mask_bits ? flash_bwd_fused_kernel<2> : flash_bwd_fused_kernel<1>)
                          : flash_bwd_fused_kernel<0>;
   DAD_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FusedSmem::kBytes));
+  // The warpgroups' register budgets add up to what a CTA is launched with only if the compiler
+  // gave the kernel kRegsLaunch registers per thread; with fewer, the compute warps' increase
+  // would wait for registers that nobody can give back. Refuse rather than hang.
+  static int regs_seen[3] = {0, 0, 0};   // per kernel variant; the same value for every device
+  int& regs = regs_seen[rate > 0.f ? (mask_bits ? 2 : 1) : 0];
+  if (regs == 0) {
+    cudaFuncAttributes fattr;
+    DAD_CUDA(cudaFuncGetAttributes(&fattr, kern));
+    regs = fattr.numRegs;
+  }
+  if (regs != kRegsLaunch)
+    return fail(DADATTN_E_UNSUPPORTED, "the single-pass backward was compiled with %d registers per thread, "
+                "its register budgets assume %d", regs, kRegsLaunch);
   DAD_CUDA(launch_pdl(kern, grid, dim3(kFThreads), FusedSmem::kBytes, st, mq, mk, mv, mdo, mws, mdk, mdv,
                       mlse, mdelta, lse_shift, item_counter, BH, S, lay.heads, group_bh, scale, rate,
                       rng, unit0, mask_bits, status));
